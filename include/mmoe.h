@@ -1,0 +1,162 @@
+/*
+ * C ABI of the B200 (sm_100a) MegaMoE expert backend: `libmmoe_b200.so`.
+ *
+ * Plain pointers, integers and a CUDA stream handle only; nothing throws across this boundary.  Every entry point
+ * returns an MMOE_* status code; `mmoe_status_string()` names it.  Device pointers are never dereferenced on the host.
+ * All kernels are enqueued on the given stream and the functions never synchronise, so a sequence of calls can be
+ * captured into a CUDA graph once `mmoe_prepare()` has run for the geometry (outside capture).
+ *
+ * Each declaration cites the interface of the reference plugin (`vllm_sm107_megamoe`, paths relative to its project
+ * root) that it stands in for.
+ */
+#ifndef MMOE_B200_H_
+#define MMOE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MMOE_OK = 0,
+  MMOE_ERR_INVALID_ARGUMENT = 1,  /* maps to AssertionError / ValueError on the Python side */
+  MMOE_ERR_UNSUPPORTED = 2,       /* maps to NotImplementedError */
+  MMOE_ERR_CUDA = 3,              /* a CUDA runtime / driver call failed: RuntimeError */
+  MMOE_ERR_ARCH = 4,              /* the current device is not compute capability 10.0: RuntimeError */
+  MMOE_ERR_NOT_PREPARED = 5,      /* a launch was requested before mmoe_prepare(): RuntimeError */
+  MMOE_ERR_DEVICE_TIMEOUT = 6     /* a bounded device-side wait expired (read back with mmoe_read_status) */
+};
+
+/* Geometry of one layer instance on one rank.  Replaces the positional geometry arguments of
+ * `get_symm_buffer_for_mega_moe` (api.py:39-65) and of the kernel configuration (backend/config.py:41-329). */
+typedef struct MmoeGeometry {
+  int32_t num_ranks;           /* expert-parallel size R (1..32) */
+  int32_t rank;                /* this rank */
+  int32_t num_experts;         /* physical routed experts over all ranks (E); this rank owns [rank*E/R, (rank+1)*E/R) */
+  int32_t num_topk;            /* routes per token (k) */
+  int32_t hidden;              /* H */
+  int32_t intermediate;        /* I */
+  int32_t num_shared_experts;  /* 0 or 1 */
+  int32_t num_max_tokens;      /* per-rank token capacity T, a multiple of 1920 */
+} MmoeGeometry;
+
+/* Byte offsets of every region of the per-rank workspace (one allocation owned by the caller).  The first five are the
+ * views the serving engine writes or reads (`SymmBuffer.x / x_sf / topk_idx / topk_weights / shared_l1_acts_sf`,
+ * backend/workspace.py:72-76,147-161); the rest are private to the kernels.  Replaces `build_symm_buffer_layout`
+ * (backend/heuristics.py:504-674). */
+typedef struct MmoeLayout {
+  int64_t total_bytes;
+  int64_t x;                /* e4m3 [T, H] */
+  int64_t x_sf;             /* int32 [T, H/128], byte j of word w = UE8M0 exponent of K group 4w+j */
+  int64_t topk_idx;         /* int64 [T, k], -1 = masked */
+  int64_t topk_weights;     /* float [T, k] */
+  int64_t shared_x_sf;      /* int32 [ceil(T/8)*128, H/128], element (row, word) at word*rows + row */
+  int64_t shared_sf_rows;   /* = ceil(T/8)*128 */
+  int64_t send_count;       /* int32 [E]      routes of this rank per destination physical expert */
+  int64_t send_offset;      /* int32 [E+1]    exclusive prefix of send_count */
+  int64_t route_pos;        /* int32 [T*k]    position of a route in send order, -1 = masked */
+  int64_t sorted_route;     /* int32 [T*k]    route id (token*k + slot) at each send position */
+  int64_t sort_scratch;     /* int32 [ceil(T/128), E] per-chunk expert counts of the route ordering */
+  int64_t recv_count;       /* int32 [R, E/R] routes received per (source rank, local expert) */
+  int64_t plan;             /* MmoePlanHeader followed by per-expert and per-tile tables */
+  int64_t send_x, send_sf, send_w;      /* EP>1 only: packed rows in send order */
+  int64_t recv_x, recv_sf, recv_w;      /* EP>1 only: rows in receive order */
+  int64_t pool_x;           /* e4m3 [pool_rows, H] */
+  int64_t pool_sf;          /* int32 chunks, element (chunk row, word) at word*pool_sf_rows + row */
+  int64_t pool_w;           /* float [pool_rows] top-k weight of each pool row */
+  int64_t pool_dst;         /* int32 [pool_rows] row of `ret` that receives the expert output, -1 = padding */
+  int64_t act_x;            /* e4m3 [pool_rows, I]   SwiGLU output of the routed experts */
+  int64_t act_sf;           /* int32 chunks like pool_sf with I/128 words */
+  int64_t shared_act_x;     /* e4m3 [T, I] */
+  int64_t shared_act_sf;    /* int32 chunks like shared_x_sf with I/128 words */
+  int64_t ret;              /* bf16 [R*T*kmax, H]  expert outputs in receive order (EP1: == send order) */
+  int64_t ret_recv;         /* EP>1 only: bf16 [T*kmax, H] outputs returned to this rank, in send order */
+  int64_t shared_out;       /* bf16 [T, H] */
+  int64_t status;           /* int32 [8] device status words, zero = healthy */
+  int64_t pool_rows;        /* row capacity of pool_x / act_x */
+  int64_t pool_sf_rows;     /* row capacity (multiple of 128) of the pool SF chunk matrices */
+  int64_t max_routes;       /* T * min(k, E/R): rows one rank can send */
+  int64_t max_tiles;        /* capacity of the tile table */
+} MmoeLayout;
+
+/* Replaces `build_symm_buffer_layout` (backend/heuristics.py:504-674) / `SymmBuffer.__init__` sizing
+ * (backend/workspace.py:108-116). */
+int mmoe_layout(const MmoeGeometry* geo, MmoeLayout* out);
+
+/* Replaces `get_block_m_for_mega_moe` (api.py:103-118; backend/heuristics.py:123-197). */
+int mmoe_block_m(int32_t num_ranks, int32_t num_experts, int32_t num_tokens, int32_t num_topk);
+
+/* Load the kernels of every BLOCK_M variant, raise their dynamic shared-memory limits and resolve the driver entry
+ * points used for tensor maps.  Must run once per process and device before any launch and outside stream capture.
+ * Replaces `precompile_mega_moe_variants` (api.py:179-206; backend/frontend.py:851-897) and the JIT cache
+ * (backend/jit.py:350-395).  `block_ms` receives the prepared variants (capacity `cap`), `*n` their number. */
+int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_t* n);
+
+/* Kernel (a): BF16 hidden states -> MXFP8 E4M3 + packed UE8M0 scales, routing repack (padding -> id -1 / weight 0) and
+ * the shared-expert scale scatter, written into the workspace views.  Replaces `prepare_megamoe_inputs`
+ * (backend/staging.py:152-251) and its Triton kernel (backend/staging_triton.py:23-226).
+ * `topk_ids` may be int32 or int64 (`ids_are_int64`); `is_padding` (uint8 per token) and the shared view are optional
+ * (`shared_block_m <= 0` skips the scatter). */
+int mmoe_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidden_bf16, const void* topk_ids,
+                      int32_t ids_are_int64, const float* topk_weights, const uint8_t* is_padding, int32_t num_tokens,
+                      int32_t shared_block_m, void* stream);
+
+/* Weights of one rank in the layout `transform_weights_for_mega_moe` of this backend produces. */
+typedef struct MmoeWeights {
+  const void* w13;        /* packed E2M1 [E/R, 2I, H/2], rows [gate | up] */
+  const void* w13_sf;     /* int32 [E/R, H/128, 2I] (scale word w of row r at w*2I + r'), 4x32 transposed per 128 rows */
+  const void* w2;         /* packed E2M1 [E/R, H, I/2] */
+  const void* w2_sf;      /* int32 [E/R, I/128, H], 4x32 transposed per 128 rows */
+  const void* shared_w13; /* E4M3 [2I, H] or NULL */
+  const void* shared_w13_sf;
+  const void* shared_w2;  /* E4M3 [H, I] or NULL */
+  const void* shared_w2_sf;
+  /* Routed weights may be given in the two-slice form `localize()` produces (backend/locality.py:573-587 of the
+   * reference): [2, E/R, N/2, K/2] with the two slices `*_slice_stride` bytes apart, slice s holding rows
+   * [s*N/2, (s+1)*N/2) of every expert.  A stride of 0 means the plain [E/R, N, K/2] tensor. */
+  int64_t w13_slice_stride;
+  int64_t w2_slice_stride;
+} MmoeWeights;
+
+typedef struct MmoeOptions {
+  float activation_clamp;   /* SwiGLU clamp; +inf disables it */
+  int32_t fast_math;        /* 1: ex2.approx / rcp.approx sigmoid, 0: IEEE expf and division */
+  int32_t engine;           /* 0: tcgen05 tensor-core kernels; 1: scalar validation kernels (tests only) */
+  int32_t timeout_ms;       /* bound of every device-side wait; <= 0 selects the default (2000) */
+} MmoeOptions;
+
+/* The steps of one forward call.  At EP1 `mmoe_forward` runs all of them; at EP>1 the host interleaves the three
+ * exchanges (counts, rows out, rows back) between them.  Together they replace `fp8_fp4_mega_moe`
+ * (api.py:78-100; backend/frontend.py:627-848) and the device roles it launches (backend/kernel/dispatch.py,
+ * scheduler.py, tma_warps.py, mma_warp.py, epilogue.py, combine.py). */
+
+/* Count this rank's routes per destination expert and order them (send order = by expert, token, slot). */
+int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream);
+/* EP>1: gather rows, scales and weights into send order. */
+int mmoe_dispatch_pack(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream);
+/* Build the pool plan from `recv_count`, place received rows into the BLOCK_M-aligned pool, add the per-expert totals
+ * to `stats` (int32 [E/R], may be NULL).  `total_recv_rows` bounds the rows present in receive order. */
+int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, int32_t block_m,
+                        int32_t* stats, void* stream);
+/* Grouped GEMM1 -> SwiGLU/requant -> grouped GEMM2 for routed and shared experts. */
+int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
+                 int32_t num_tokens, int32_t block_m, void* stream);
+/* y[t] = bf16(sum of the token's valid slots in ascending order, shared expert last). */
+int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream);
+/* EP1 convenience: count, place, experts, combine. */
+int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
+                 void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream);
+
+/* Copy the device status words to the host (synchronises the stream) and translate them: MMOE_OK or
+ * MMOE_ERR_DEVICE_TIMEOUT.  Replaces the reference's device `trap` after a 300 s spin (backend/kernel/comm.py:229-250). */
+int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream);
+
+const char* mmoe_status_string(int code);
+const char* mmoe_last_error(void);   /* detail of the last failure on this thread */
+int mmoe_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MMOE_B200_H_ */

@@ -1,0 +1,247 @@
+"""``fp8_fp4_mega_moe`` and its companions: host-side checks, BLOCK_M selection, variant preparation and the launch
+sequence of one forward call.  Mirrors ``backend/frontend.py`` of the reference (``KernelOptions`` :72-116,
+``get_block_m_for_mega_moe`` :157-171, ``check_mega_moe_arguments`` :437-623, ``fp8_fp4_mega_moe`` :627-848,
+``precompile_mega_moe_variants`` :851-897) on top of the C ABI of ``libmmoe_b200.so``.
+
+At EP = 1 one call is: route ordering -> pool placement -> grouped GEMM1 (+SwiGLU/requant) -> grouped GEMM2 -> combine.
+At EP > 1 three NCCL exchanges sit between those steps (per-expert counts, rows out, rows back), issued through
+``torch.distributed`` on the caller's group; the expert shards need no other collective.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import math
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+
+from . import _native
+from . import heuristics as _h
+
+
+@dataclasses.dataclass(frozen=True)
+class KernelOptions:
+    """Process-wide launch options (the reference keeps every tuning knob an explicit field, never an environment
+    variable: ``backend/frontend.py:72-116``)."""
+
+    block_m: int = 0          # > 0 forces the BLOCK_M variant
+    timeout_ms: int = 2000    # bound of every device-side wait
+    engine: int = _native.ENGINE_TENSOR_CORE   # ENGINE_SCALAR_VALIDATION selects the scalar validation kernels (tests)
+
+
+_kernel_options = KernelOptions()
+_prepared: Dict[Tuple, Tuple[int, ...]] = {}
+
+
+def set_kernel_options(**kwargs: Any) -> KernelOptions:
+    global _kernel_options
+    _kernel_options = dataclasses.replace(_kernel_options, **kwargs)
+    if _kernel_options.block_m and _kernel_options.block_m not in _h.VALID_BLOCK_MS:
+        raise AssertionError(f"block_m={_kernel_options.block_m} is not one of {_h.VALID_BLOCK_MS}")
+    return _kernel_options
+
+
+def get_kernel_options() -> KernelOptions:
+    return _kernel_options
+
+
+def require_sm100() -> None:
+    """The kernels are compiled for sm_100a only (the reference gates on its own architecture the same way,
+    ``backend/frontend.py:261-270``)."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("The B200 MegaMoE backend needs a CUDA device of compute capability 10.0; none is visible.")
+    cc = tuple(torch.cuda.get_device_capability())
+    if cc != (10, 0):
+        raise RuntimeError(f"The B200 MegaMoE backend needs compute capability 10.0 (sm_100a), got {cc[0]}.{cc[1]}.")
+
+
+def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_tokens: int,
+                             num_topk: int, mma_type: str = "fp8xfp4") -> int:
+    if _kernel_options.block_m > 0:
+        return _kernel_options.block_m
+    return _h.get_block_m_for_mega_moe(num_ranks, num_experts, num_max_tokens_per_rank, num_tokens, num_topk, mma_type)
+
+
+def precompile_mega_moe_variants(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
+                                 hidden: int, intermediate_hidden: int, num_shared_experts: int = 0, *,
+                                 activation_clamp: Optional[float] = None, activation_alpha: float = 1.0,
+                                 activation_beta: float = 0.0, fast_math: bool = True, per_die: bool = False,
+                                 localized_weights: bool = False, localized_shared_weights: bool = False
+                                 ) -> Tuple[int, ...]:
+    """Make every BLOCK_M variant the geometry can reach launchable (kernel images loaded, shared-memory limits raised,
+    tensor-map encoder resolved) and return them.  Must run outside CUDA-graph capture; calls after the first are free."""
+    require_sm100()
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("MegaMoE variants must be prepared before CUDA-graph capture")
+    if activation_alpha != 1.0 or activation_beta != 0.0:
+        raise NotImplementedError("activation_alpha / activation_beta other than (1, 0) are not supported")
+    if localized_shared_weights:
+        raise NotImplementedError("localized shared-expert weights are not supported")
+    t = _h.align(num_max_tokens_per_rank, _h.TOKEN_ALIGNMENT)
+    key = (torch.cuda.current_device(), num_ranks, num_experts, t, num_topk, hidden, intermediate_hidden, num_shared_experts)
+    if key in _prepared:
+        return _prepared[key]
+    geo = _native.MmoeGeometry(num_ranks, 0, num_experts, num_topk, hidden, intermediate_hidden, num_shared_experts, t)
+    out = (ctypes.c_int32 * 8)()
+    n = ctypes.c_int32(0)
+    _native.check(_native.load().mmoe_prepare(ctypes.byref(geo), out, 8, ctypes.byref(n)))
+    variants = tuple(int(out[i]) for i in range(n.value))
+    assert variants == _h.get_block_m_variants(num_ranks, num_experts, num_topk, t), "host and library disagree on the variants"
+    _prepared[key] = variants
+    return variants
+
+
+def built_block_ms(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
+                   intermediate_hidden: int, num_shared_experts: int = 0) -> Tuple[int, ...]:
+    t = _h.align(num_max_tokens_per_rank, _h.TOKEN_ALIGNMENT)
+    key = (torch.cuda.current_device(), num_ranks, num_experts, t, num_topk, hidden, intermediate_hidden, num_shared_experts)
+    return _prepared.get(key, ())
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# argument checks (the reference's host asserts raise AssertionError)
+# ---------------------------------------------------------------------------------------------------------------------
+def _split_weights(w: torch.Tensor, what: str, e_l: int, n: int, k_packed: int) -> Tuple[torch.Tensor, int]:
+    """Accept the plain ``(E_l, N, K/2)`` tensor or the two-slice ``(2, E_l, N/2, K/2)`` one; return (tensor, slice stride)."""
+    assert w.dtype in (torch.int8, torch.uint8), f"{what} must be packed FP4 in int8"
+    if w.dim() == 3:
+        assert tuple(w.shape) == (e_l, n, k_packed) and w.is_contiguous(), f"{what}: expected contiguous {(e_l, n, k_packed)}, got {tuple(w.shape)}"
+        return w, 0
+    assert w.dim() == 4 and tuple(w.shape) == (2, e_l, n // 2, k_packed), f"{what}: expected {(2, e_l, n // 2, k_packed)}, got {tuple(w.shape)}"
+    assert w[0].is_contiguous() and w[1].is_contiguous(), f"{what}: each slice must be contiguous"
+    return w, w.stride(0) * w.element_size()
+
+
+def _check_sf(sf: torch.Tensor, what: str, lead: Tuple[int, ...], n: int, k: int) -> None:
+    assert sf.dtype == torch.int32, f"{what} must be int32 (four UE8M0 bytes per word)"
+    assert tuple(sf.shape) == lead + (n, k // 128), f"{what}: expected {lead + (n, k // 128)}, got {tuple(sf.shape)}"
+    assert sf.stride(-2) == 1 and sf.stride(-1) == n, f"{what} must be dense MN-major (stride(-2) == 1, stride(-1) == rows)"
+    if lead:
+        assert sf.stride(0) == n * (k // 128), f"{what}: experts must be contiguous"
+
+
+def check_mega_moe_arguments(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights, stats, recipe,
+                             activation, activation_clamp, fast_math, activation_alpha, activation_beta):
+    assert tuple(recipe) == (1, 1, 32), f"unsupported recipe {recipe}"
+    assert activation == "swiglu", f"unsupported activation {activation!r}"
+    if activation_alpha != 1.0 or activation_beta != 0.0:
+        raise NotImplementedError("activation_alpha / activation_beta other than (1, 0) are not supported")
+    h, inter = sym_buffer.hidden, sym_buffer.intermediate_hidden
+    r = sym_buffer.num_ranks
+    assert r <= _h.MAX_RANKS
+    e_l = sym_buffer.num_experts // r
+    m = y.size(0)
+    assert y.dim() == 2 and y.size(1) == h and y.dtype == torch.bfloat16 and y.is_contiguous(), "y must be contiguous BF16 (M, H)"
+    assert y.is_cuda and y.data_ptr() % 16 == 0, "y must be a 16-byte aligned CUDA tensor"
+    assert m <= sym_buffer.num_max_tokens_per_rank, "num_tokens must be <= num_max_tokens_per_rank"
+    w13, s13 = _split_weights(l1_weights[0], "l1 weights", e_l, 2 * inter, h // 2)
+    w2, s2 = _split_weights(l2_weights[0], "l2 weights", e_l, h, inter // 2)
+    _check_sf(l1_weights[1], "l1 scale factors", (e_l,), 2 * inter, h)
+    _check_sf(l2_weights[1], "l2 scale factors", (e_l,), h, inter)
+    n_shared = sym_buffer.num_shared_experts
+    assert n_shared <= _h.MAX_SHARED_EXPERTS
+    assert (shared_l1_weights is None) == (shared_l2_weights is None)
+    assert (shared_l1_weights is not None) == (n_shared > 0), "shared expert weights must be given iff the buffer has a shared expert"
+    if shared_l1_weights is not None:
+        sw13, ssf13 = shared_l1_weights
+        sw2, ssf2 = shared_l2_weights
+        assert sw13.dtype == torch.float8_e4m3fn and tuple(sw13.shape) == (2 * inter * n_shared, h) and sw13.is_contiguous()
+        assert sw2.dtype == torch.float8_e4m3fn and tuple(sw2.shape) == (h, inter * n_shared) and sw2.is_contiguous()
+        _check_sf(ssf13, "shared l1 scale factors", (), 2 * inter, h)
+        _check_sf(ssf2, "shared l2 scale factors", (), h, inter)
+    if stats is not None:
+        assert stats.dtype == torch.int32 and stats.numel() == e_l and stats.is_contiguous() and stats.is_cuda
+    if activation_clamp is not None:
+        assert activation_clamp > 0, "activation_clamp must be positive"
+    assert isinstance(fast_math, (bool, int))
+    return s13, s2
+
+
+def _weights_struct(l1, l2, sl1, sl2, s13: int, s2: int) -> _native.MmoeWeights:
+    w = _native.MmoeWeights()
+    w.w13, w.w13_sf = l1[0].data_ptr(), l1[1].data_ptr()
+    w.w2, w.w2_sf = l2[0].data_ptr(), l2[1].data_ptr()
+    if sl1 is not None:
+        w.shared_w13, w.shared_w13_sf = sl1[0].data_ptr(), sl1[1].data_ptr()
+        w.shared_w2, w.shared_w2_sf = sl2[0].data_ptr(), sl2[1].data_ptr()
+    w.w13_slice_stride, w.w2_slice_stride = s13, s2
+    return w
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# EP > 1 exchanges (NCCL all-to-allv through torch.distributed); device-agnostic so that the host logic is testable
+# with gloo ranks on CPU tensors
+# ---------------------------------------------------------------------------------------------------------------------
+def exchange_counts(group, send_count: torch.Tensor, recv_count: torch.Tensor) -> Tuple[list, list]:
+    """``send_count`` int32 ``[E]`` (routes of this rank per destination physical expert) -> ``recv_count`` int32
+    ``[R, E_l]`` (per source rank and local expert).  Returns the per-peer row counts ``(send_splits, recv_splits)``."""
+    import torch.distributed as dist
+    r = group.size()
+    dist.all_to_all_single(recv_count.view(-1), send_count.view(-1), group=group)
+    send_splits = send_count.view(r, -1).sum(dim=1).tolist()
+    recv_splits = recv_count.view(r, -1).sum(dim=1).tolist()
+    return send_splits, recv_splits
+
+
+def exchange_rows(group, dst: torch.Tensor, src: torch.Tensor, dst_splits, src_splits) -> None:
+    """All-to-allv of whole rows: peer ``p`` gets ``src_splits[p]`` consecutive rows of ``src`` and contributes
+    ``dst_splits[p]`` consecutive rows of ``dst`` (source ranks ascending)."""
+    import torch.distributed as dist
+    n_src, n_dst = sum(src_splits), sum(dst_splits)
+    s = src[:n_src]
+    d = dst[:n_dst]
+    if s.dtype == torch.float8_e4m3fn:
+        s, d = s.view(torch.uint8), d.view(torch.uint8)
+    dist.all_to_all_single(d, s, list(dst_splits), list(src_splits), group=group)
+
+
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared_l1_weights=None, shared_l2_weights=None,
+                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                     recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
+                     activation_clamp: Optional[float] = None, fast_math: bool = True, activation_alpha: float = 1.0,
+                     activation_beta: float = 0.0) -> None:
+    """One MegaMoE layer call for this rank: reads the staged inputs of ``sym_buffer`` (first ``y.size(0)`` tokens),
+    writes ``y``.  Launches on the current stream and never synchronises at EP = 1."""
+    require_sm100()
+    s13, s2 = check_mega_moe_arguments(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights,
+                                       cumulative_local_expert_recv_stats, recipe, activation, activation_clamp,
+                                       fast_math, activation_alpha, activation_beta)
+    lib = _native.load()
+    geo = sym_buffer.geo
+    m = y.size(0)
+    bm = get_block_m_for_mega_moe(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank, m,
+                                  sym_buffer.num_topk, sym_buffer.mma_type)
+    opts = _native.MmoeOptions(float(activation_clamp) if activation_clamp is not None else math.inf,
+                               1 if fast_math else 0, _kernel_options.engine, _kernel_options.timeout_ms)
+    if opts.engine == _native.ENGINE_TENSOR_CORE:
+        precompile_mega_moe_variants(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank,
+                                     sym_buffer.num_topk, sym_buffer.hidden, sym_buffer.intermediate_hidden,
+                                     sym_buffer.num_shared_experts) if not torch.cuda.is_current_stream_capturing() else None
+    w = _weights_struct(l1_weights, l2_weights, shared_l1_weights, shared_l2_weights, s13, s2)
+    stats_ptr = cumulative_local_expert_recv_stats.data_ptr() if cumulative_local_expert_recv_stats is not None else None
+    stream = torch.cuda.current_stream(y.device).cuda_stream
+    ws = sym_buffer.base_ptr
+    g = ctypes.byref(geo)
+    if sym_buffer.num_ranks == 1:
+        _native.check(lib.mmoe_forward(g, ws, ctypes.byref(w), ctypes.byref(opts), y.data_ptr(), m, bm, stats_ptr, stream))
+        return
+    group = sym_buffer.group
+    _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
+    _native.check(lib.mmoe_dispatch_pack(g, ws, m, stream))
+    send_splits, recv_splits = exchange_counts(group, sym_buffer.send_count, sym_buffer.recv_count)
+    exchange_rows(group, sym_buffer.recv_x, sym_buffer.send_x, recv_splits, send_splits)
+    exchange_rows(group, sym_buffer.recv_sf, sym_buffer.send_sf, recv_splits, send_splits)
+    exchange_rows(group, sym_buffer.recv_w, sym_buffer.send_w, recv_splits, send_splits)
+    _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
+    _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
+    exchange_rows(group, sym_buffer.ret_recv, sym_buffer.ret, send_splits, recv_splits)
+    _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
+
+
+def read_status(sym_buffer) -> None:
+    """Synchronise and raise if a device-side wait expired or the dispatch saw an out-of-range expert id."""
+    words = (ctypes.c_int32 * 8)()
+    stream = torch.cuda.current_stream(sym_buffer.device).cuda_stream
+    _native.check(_native.load().mmoe_read_status(ctypes.byref(sym_buffer.geo), sym_buffer.base_ptr, words, stream))

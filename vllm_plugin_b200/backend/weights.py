@@ -1,0 +1,82 @@
+"""Weight layout of the B200 MegaMoE kernels (``transform_weights_for_mega_moe``).
+
+Input contract = the reference's (``backend/weights.py:5-13``): L1 weights ``(E_l, 2I, H/2)`` int8, two E2M1 values per
+byte with the low nibble holding the even K index, rows ``[gate | up]``; L2 weights ``(E_l, H, I/2)``; scale factors
+int32 ``(E_l, N, ceil(K/128))`` with four UE8M0 bytes per word (byte ``b`` of word ``w`` = K group ``4w + b``) stored
+MN-major (``stride(-2) == 1``), which is what :func:`sf_to_required_layout` produces from per-32 scales
+(``backend/weights.py:37-80``).
+
+Output = what the sm_100a kernels read.  The packed weights are left exactly as given: gate and up rows of a channel
+tile go to two separate tensor-memory accumulators, so no row interleave is needed (the reference interleaves eight
+rows, ``backend/weights.py:83-97``).  The scale words get the 4x32 transpose inside every 128-row block (stored position
+``4c + a`` holds row ``32a + c``, same as ``backend/weights.py:100-117``) so that each (128 rows, 128 K) block of scales
+is one contiguous 512-byte chunk in the order ``tcgen05.cp`` copies into tensor memory.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple, Union
+
+import torch
+
+_SUPPORTED_ACTIVATIONS = ("swiglu",)
+
+
+def _align(x: int, a: int) -> int:
+    return -(-x // a) * a
+
+
+def sf_to_required_layout(sf: torch.Tensor, mn: int, k: int, num_groups: Optional[int] = None) -> torch.Tensor:
+    """Per-32-K UE8M0 scales (float32 powers of two or uint8 exponent bytes, ``([G,] mn, ceil(k/32))``) -> int32
+    ``([G,] mn, ceil(k/128))``, MN-major (strides ``(ceil(k/128) * align(mn, 4), 1, align(mn, 4))``)."""
+    assert sf.dim() == (3 if num_groups is not None else 2), "expected ([G,] mn, k/32) scales"
+    squeeze = num_groups is None
+    if squeeze:
+        sf = sf.unsqueeze(0)
+    g, n, k32 = sf.shape
+    assert n == mn and k32 == -(-k // 32), f"scale shape {tuple(sf.shape)} does not match mn={mn}, k={k}"
+    if num_groups is not None:
+        assert g == num_groups
+    if sf.dtype == torch.uint8:
+        bytes_ = sf
+    else:
+        assert sf.dtype == torch.float32, "scales must be float32 (UE8M0 values) or uint8 (E8M0 bytes)"
+        bits = sf.view(torch.int32)
+        assert (bits >= 0).all() and (bits & 0x7FFFFF == 0).all(), "float32 scales must be non-negative powers of two"
+        bytes_ = (bits >> 23).to(torch.uint8)
+    k128 = -(-k32 // 4)
+    if k32 % 4:
+        bytes_ = torch.nn.functional.pad(bytes_, (0, k128 * 4 - k32), value=127)
+    packed = bytes_.contiguous().view(torch.int32)
+    n4 = _align(mn, 4)
+    out = torch.empty_strided((g, mn, k128), (k128 * n4, 1, n4), dtype=torch.int32, device=sf.device)
+    out.copy_(packed)
+    return out.squeeze(0) if squeeze else out
+
+
+def transpose_sf_for_utccp(sf: torch.Tensor) -> torch.Tensor:
+    """4x32 transpose of int32 scale words ``([G,] MN, K/128)`` inside every 128-row block; keeps the input strides."""
+    assert sf.dtype == torch.int32 and sf.dim() in (2, 3)
+    squeeze = sf.dim() == 2
+    if squeeze:
+        sf = sf.unsqueeze(0)
+    g, mn, kw = sf.shape
+    assert mn % 128 == 0, "scale rows must be a multiple of 128"
+    res = sf.reshape(g, -1, 4, 32, kw).transpose(2, 3).reshape(g, mn, kw)
+    out = torch.empty_like(sf).copy_(res)
+    return out.squeeze(0) if squeeze else out
+
+
+def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                                   l2_weights: Tuple[torch.Tensor, torch.Tensor], activation: str = "swiglu"
+                                   ) -> Tuple[Tuple[torch.Tensor, torch.Tensor], Tuple[torch.Tensor, torch.Tensor]]:
+    """``(weights, sf)`` pairs in, ``(weights, sf)`` pairs out; shared-expert pairs (2-D tensors) go through the same
+    function.  The weight tensors are returned unchanged (same storage), only the scale words are rearranged."""
+    assert activation in _SUPPORTED_ACTIVATIONS, f"Activation must be one of {_SUPPORTED_ACTIVATIONS}, got `{activation}`"
+    if not isinstance(l1_weights, tuple) or not isinstance(l2_weights, tuple):
+        raise NotImplementedError("only (weights, scale factors) pairs are supported (MXFP4 / MXFP8 weights)")
+    for w, sf in (l1_weights, l2_weights):
+        assert sf.dtype == torch.int32, "scale factors must be packed int32 words"
+        assert sf.stride(-2) == 1, "scale factors must be MN-major (stride(-2) == 1)"
+        assert w.shape[-2] == sf.shape[-2], "weights and scale factors disagree on the row count"
+    return (l1_weights[0], transpose_sf_for_utccp(l1_weights[1])), (l2_weights[0], transpose_sf_for_utccp(l2_weights[1]))

@@ -1,0 +1,353 @@
+// extern "C" entry points of libmmoe_b200.so (declared in include/mmoe.h): argument checks, workspace layout, and the
+// sequencing of the kernels of one forward call.  Nothing here allocates device memory or synchronises.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+
+#include "mmoe_common.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(MMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+const int kBlockMs[6] = {16, 32, 64, 128, 192, 240};
+bool g_prepared = false;
+
+bool valid_block_m(int bm) {
+  for (int v : kBlockMs)
+    if (v == bm) return true;
+  return false;
+}
+
+int check_geometry(const MmoeGeometry* g) {
+  if (g == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "geometry is NULL");
+  if (g->num_ranks < 1 || g->num_ranks > 32) return fail(MMOE_ERR_INVALID_ARGUMENT, "num_ranks=%d outside [1, 32]", g->num_ranks);
+  if (g->rank < 0 || g->rank >= g->num_ranks) return fail(MMOE_ERR_INVALID_ARGUMENT, "rank=%d outside [0, %d)", g->rank, g->num_ranks);
+  if (g->num_experts < 1 || g->num_experts % g->num_ranks != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "num_experts=%d must be a positive multiple of num_ranks=%d", g->num_experts, g->num_ranks);
+  if (g->num_experts > 2048 || g->num_experts / g->num_ranks > 512)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "num_experts=%d exceeds 2048 (or 512 per rank)", g->num_experts);
+  if (g->num_topk < 1 || g->num_topk > 31) return fail(MMOE_ERR_INVALID_ARGUMENT, "num_topk=%d outside [1, 31]", g->num_topk);
+  if (g->hidden < 256 || g->hidden % 256 != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "hidden=%d must be a multiple of 256", g->hidden);
+  if (g->intermediate < 128 || g->intermediate % 128 != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "intermediate=%d must be a multiple of 128", g->intermediate);
+  if (g->num_shared_experts < 0 || g->num_shared_experts > 1)
+    return fail(MMOE_ERR_UNSUPPORTED, "num_shared_experts=%d (supported: 0 or 1)", g->num_shared_experts);
+  if (g->num_max_tokens < 1920 || g->num_max_tokens % 1920 != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "num_max_tokens=%d must be a positive multiple of 1920", g->num_max_tokens);
+  return MMOE_OK;
+}
+
+int make_ctx(const MmoeGeometry* g, void* ws, mmoe::Ctx* c) {
+  int rc = check_geometry(g);
+  if (rc != MMOE_OK) return rc;
+  if (ws == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "workspace is NULL");
+  if ((reinterpret_cast<uintptr_t>(ws) & 1023u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "workspace must be 1024-byte aligned");
+  c->geo = *g;
+  rc = mmoe_layout(g, &c->lay);
+  if (rc != MMOE_OK) return rc;
+  c->ws = static_cast<char*>(ws);
+  c->e_local = g->num_experts / g->num_ranks;
+  c->kmax = g->num_topk < c->e_local ? g->num_topk : c->e_local;
+  return MMOE_OK;
+}
+
+int check_tokens(const MmoeGeometry* g, int m) {
+  if (m < 0 || m > g->num_max_tokens) return fail(MMOE_ERR_INVALID_ARGUMENT, "num_tokens=%d outside [0, %d]", m, g->num_max_tokens);
+  return MMOE_OK;
+}
+
+float bf16_round_host(float v) {
+  if (isinf(v) || isnan(v)) return v;
+  uint32_t b;
+  memcpy(&b, &v, 4);
+  b = (b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u;
+  memcpy(&v, &b, 4);
+  return v;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mmoe_abi_version(void) { return 1; }
+
+const char* mmoe_last_error(void) { return g_last_error.c_str(); }
+
+const char* mmoe_status_string(int code) {
+  switch (code) {
+    case MMOE_OK: return "ok";
+    case MMOE_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case MMOE_ERR_UNSUPPORTED: return "unsupported option";
+    case MMOE_ERR_CUDA: return "CUDA call failed";
+    case MMOE_ERR_ARCH: return "device is not compute capability 10.0 (B200)";
+    case MMOE_ERR_NOT_PREPARED: return "mmoe_prepare() has not run";
+    case MMOE_ERR_DEVICE_TIMEOUT: return "a device-side wait expired";
+    default: return "unknown status";
+  }
+}
+
+int mmoe_block_m(int32_t num_ranks, int32_t num_experts, int32_t num_tokens, int32_t num_topk) {
+  if (num_ranks <= 0 || num_experts <= 0 || num_tokens < 0) return -1;
+  // float32 arithmetic, evaluated left to right (backend/heuristics.py:140-157 of the reference)
+  volatile float e = static_cast<float>(num_tokens);
+  e = e * static_cast<float>(num_ranks);
+  e = e * static_cast<float>(num_topk);
+  e = e / static_cast<float>(num_experts);
+  volatile float root = sqrtf(e);
+  volatile float covered = e + root;
+  if (e <= 10.f) return 16;
+  if (e <= 24.f) return 32;
+  volatile float q = covered / 240.f;
+  int blocks = static_cast<int>(ceilf(q));
+  if (blocks == 1 && covered > 192.f && num_experts / num_ranks < 14) blocks = 2;
+  const int cand[4] = {64, 128, 192, 240};
+  for (int c : cand)
+    if (static_cast<float>(blocks * c) >= covered) return c;
+  return 240;
+}
+
+int mmoe_layout(const MmoeGeometry* g, MmoeLayout* out) {
+  int rc = check_geometry(g);
+  if (rc != MMOE_OK) return rc;
+  if (out == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "layout output is NULL");
+  memset(out, 0, sizeof *out);
+  const int64_t T = g->num_max_tokens, H = g->hidden, I = g->intermediate, k = g->num_topk, R = g->num_ranks;
+  const int64_t E = g->num_experts, El = E / R;
+  const int64_t kmax = k < El ? k : El;
+  const int64_t max_routes = T * kmax;          // rows one rank can send
+  const int64_t max_recv = R * max_routes;      // rows one rank can receive
+  int64_t pool_rows = 0, sf_rows = 0;
+  for (int bm : kBlockMs) {
+    const int64_t blocks = max_recv / bm + El;
+    pool_rows = blocks * bm > pool_rows ? blocks * bm : pool_rows;
+    const int64_t rows = blocks * ((bm + 127) / 128) * 128;
+    sf_rows = rows > sf_rows ? rows : sf_rows;
+  }
+  pool_rows += 128;                              // a tile box may start up to 128 rows before the end of the last block
+  const int64_t shared_rows = (T + 7) / 8 * 128;
+  const int64_t max_tiles = (max_recv / 16 + El) * 2 + (T / 16 + 2) * 2;
+  const bool ep = R > 1;
+  const bool shared = g->num_shared_experts > 0;
+
+  int64_t off = 0;
+  auto take = [&off](int64_t bytes) {
+    const int64_t at = off;
+    off = mmoe::align_up(off + (bytes > 0 ? bytes : 0), 1024);
+    return at;
+  };
+  out->x = take(T * H);
+  out->x_sf = take(T * (H / 128) * 4);
+  out->topk_idx = take(T * k * 8);
+  out->topk_weights = take(T * k * 4);
+  out->shared_sf_rows = shared_rows;
+  out->shared_x_sf = take(shared ? shared_rows * (H / 128) * 4 : 0);
+  out->send_count = take(E * 4);
+  out->send_offset = take((E + 1) * 4);
+  out->route_pos = take(T * k * 4);
+  out->sorted_route = take(T * k * 4);
+  out->sort_scratch = take(((T + 127) / 128) * E * 4);
+  out->recv_count = take(R * El * 4);
+  out->plan = take(mmoe::plan_bytes(static_cast<int>(El), static_cast<int>(R), max_tiles));
+  out->send_x = take(ep ? max_routes * H : 0);
+  out->send_sf = take(ep ? max_routes * (H / 128) * 4 : 0);
+  out->send_w = take(ep ? max_routes * 4 : 0);
+  out->recv_x = take(ep ? max_recv * H : 0);
+  out->recv_sf = take(ep ? max_recv * (H / 128) * 4 : 0);
+  out->recv_w = take(ep ? max_recv * 4 : 0);
+  out->pool_x = take(pool_rows * H);
+  out->pool_sf = take(sf_rows * (H / 128) * 4);
+  out->pool_w = take(pool_rows * 4);
+  out->pool_dst = take(pool_rows * 4);
+  out->act_x = take(pool_rows * I);
+  out->act_sf = take(sf_rows * (I / 128) * 4);
+  out->shared_act_x = take(shared ? (T + 128) * I : 0);
+  out->shared_act_sf = take(shared ? shared_rows * (I / 128) * 4 : 0);
+  out->ret = take(max_recv * H * 2);
+  out->ret_recv = take(ep ? max_routes * H * 2 : 0);
+  out->shared_out = take(shared ? T * H * 2 : 0);
+  out->status = take(64);
+  out->total_bytes = off;
+  out->pool_rows = pool_rows;
+  out->pool_sf_rows = sf_rows;
+  out->max_routes = max_routes;
+  out->max_tiles = max_tiles;
+  return MMOE_OK;
+}
+
+int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_t* n) {
+  int rc = check_geometry(geo);
+  if (rc != MMOE_OK) return rc;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  int major = 0, minor = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+  if (major != 10 || minor != 0) return fail(MMOE_ERR_ARCH, "compute capability %d.%d, need 10.0", major, minor);
+  cudaStreamCaptureStatus cap_status = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(cudaStreamPerThread, &cap_status) == cudaSuccess && cap_status != cudaStreamCaptureStatusNone)
+    return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() called during stream capture");
+  rc = mmoe::prepare_umma(*geo);
+  if (rc != MMOE_OK) return fail(rc, "loading the tensor-core kernels failed: %s", cudaGetErrorString(cudaGetLastError()));
+  g_prepared = true;
+  // every BLOCK_M the geometry can select for M in [0, T]
+  bool seen[6] = {false, false, false, false, false, false};
+  for (int m = 0; m <= geo->num_max_tokens; ++m) {
+    const int bm = mmoe_block_m(geo->num_ranks, geo->num_experts, m, geo->num_topk);
+    for (int i = 0; i < 6; ++i)
+      if (kBlockMs[i] == bm) seen[i] = true;
+  }
+  int count = 0;
+  for (int i = 0; i < 6; ++i)
+    if (seen[i]) {
+      if (block_ms != nullptr && count < cap) block_ms[count] = kBlockMs[i];
+      ++count;
+    }
+  if (n != nullptr) *n = count;
+  return MMOE_OK;
+}
+
+int mmoe_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidden_bf16, const void* topk_ids,
+                      int32_t ids_are_int64, const float* topk_weights, const uint8_t* is_padding, int32_t num_tokens,
+                      int32_t shared_block_m, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (num_tokens == 0) return MMOE_OK;
+  if (hidden_bf16 == nullptr || topk_ids == nullptr || topk_weights == nullptr)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "staging inputs must not be NULL");
+  if ((reinterpret_cast<uintptr_t>(hidden_bf16) & 15u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "hidden states must be 16-byte aligned");
+  if (shared_block_m > 0 && !valid_block_m(shared_block_m))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "shared_block_m=%d is not a BLOCK_M value", shared_block_m);
+  cudaError_t e = mmoe::launch_stage(c, hidden_bf16, topk_ids, ids_are_int64, topk_weights, is_padding, num_tokens,
+                                     shared_block_m, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "stage_inputs launch");
+}
+
+int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  cudaError_t e = mmoe::launch_count_sort(c, num_tokens, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_count launch");
+}
+
+int mmoe_dispatch_pack(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (geo->num_ranks == 1) return MMOE_OK;
+  cudaError_t e = mmoe::launch_pack(c, num_tokens, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_pack launch");
+}
+
+int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, int32_t block_m, int32_t* stats,
+                        void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
+  cudaError_t e = mmoe::launch_plan_place(c, num_tokens, block_m, stats, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_place launch");
+}
+
+int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
+                 int32_t num_tokens, int32_t block_m, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (weights == nullptr || opt == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "weights / options are NULL");
+  if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
+  if (weights->w13 == nullptr || weights->w13_sf == nullptr || weights->w2 == nullptr || weights->w2_sf == nullptr)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "routed expert weights must not be NULL");
+  if (geo->num_shared_experts > 0 && (weights->shared_w13 == nullptr || weights->shared_w13_sf == nullptr ||
+                                      weights->shared_w2 == nullptr || weights->shared_w2_sf == nullptr))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "shared expert weights must not be NULL when num_shared_experts > 0");
+  const void* aligned[] = {weights->w13, weights->w13_sf, weights->w2, weights->w2_sf, weights->shared_w13,
+                           weights->shared_w13_sf, weights->shared_w2, weights->shared_w2_sf};
+  for (const void* p : aligned)
+    if ((reinterpret_cast<uintptr_t>(p) & 31u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "weight tensors must be 32-byte aligned");
+  if (!(opt->activation_clamp > 0.f)) return fail(MMOE_ERR_INVALID_ARGUMENT, "activation_clamp must be positive (use +inf for none)");
+  MmoeOptions o = *opt;
+  o.activation_clamp = bf16_round_host(o.activation_clamp);   // the clamp is applied to BF16 values
+  cudaError_t e;
+  if (o.engine == 1) {
+    e = mmoe::launch_experts_simt(c, *weights, o, num_tokens, block_m, static_cast<cudaStream_t>(stream));
+  } else if (o.engine == 0) {
+    if (!g_prepared) return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() must run before the first launch");
+    e = mmoe::launch_experts_umma(c, *weights, o, num_tokens, block_m, static_cast<cudaStream_t>(stream));
+  } else {
+    return fail(MMOE_ERR_UNSUPPORTED, "engine=%d", o.engine);
+  }
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "experts launch");
+}
+
+int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (num_tokens > 0 && (y_bf16 == nullptr || (reinterpret_cast<uintptr_t>(y_bf16) & 15u) != 0))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "y must be a 16-byte aligned device pointer");
+  cudaError_t e = mmoe::launch_combine(c, y_bf16, num_tokens, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "combine launch");
+}
+
+int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
+                 void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream) {
+  if (geo != nullptr && geo->num_ranks != 1)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "mmoe_forward is the single-rank sequence; call the steps for num_ranks > 1");
+  int rc = mmoe_dispatch_count(geo, workspace, num_tokens, stream);
+  if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
+  if (rc == MMOE_OK) rc = mmoe_experts(geo, workspace, weights, opt, num_tokens, block_m, stream);
+  if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+  return rc;
+}
+
+int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  int32_t host[8];
+  cudaError_t e = cudaMemcpyAsync(host, c.ws + c.lay.status, sizeof host, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "reading the status words");
+  if (words8 != nullptr) memcpy(words8, host, sizeof host);
+  if (host[mmoe::kStatusTimeout] != 0)
+    return fail(MMOE_ERR_DEVICE_TIMEOUT, "device wait expired: kernel %d role %d block %d", host[mmoe::kStatusKernel],
+                host[mmoe::kStatusRole], host[mmoe::kStatusBlock]);
+  if (host[mmoe::kStatusBadIndex] != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "%d expert ids were >= num_experts", host[mmoe::kStatusBadIndex]);
+  return MMOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,175 @@
+// Shared definitions of the sm_100a MegaMoE kernels: plan tables, number-format helpers and the two epilogue
+// functions (SwiGLU + requantisation, BF16 store) that both the tcgen05 kernels and the scalar validation kernels call.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mmoe.h"
+
+namespace mmoe {
+
+constexpr int kGroupK = 32;        // K elements per UE8M0 scale
+constexpr int kTileK = 128;        // K elements per pipeline stage = one packed scale word
+constexpr int kTileRows = 128;     // weight rows per tile (UMMA M)
+constexpr int kChunkRows = 128;    // token rows per scale-factor chunk (one 512-byte tcgen05.cp source per K stage)
+constexpr int kMaxTileTokens = 112;  // largest UMMA N of one task; a fuller chunk is split into two 64-token halves
+constexpr int kSortChunkTokens = 128;
+constexpr int kSharedExpert = -2;  // MmoeTile::expert of a shared-expert tile
+
+// One unit of token rows handed to the grouped GEMMs: `n_valid` (<= 112) rows starting at `row0` of the token matrix
+// (pool rows for routed experts, token indices for the shared expert), whose scales live in chunk `sf_chunk`
+// starting at row `32 * sf_col` of that chunk.
+struct Tile {
+  int32_t expert;    // local expert index, or kSharedExpert
+  int32_t row0;
+  int32_t n_valid;
+  int32_t sf_chunk;
+  int32_t sf_col;    // 0 or 2: first 32-row group of the chunk this tile uses
+  int32_t pad[3];
+};
+static_assert(sizeof(Tile) == 32, "tile record is 32 bytes");
+
+struct PlanHeader {
+  int32_t num_routed_tiles;
+  int32_t num_shared_tiles;
+  int32_t num_pool_blocks;     // sum over experts of ceil(n_e / BLOCK_M)
+  int32_t total_recv;          // routes received by this rank
+  int32_t block_m;
+  int32_t num_tokens;
+  int32_t pad[10];
+};
+static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
+
+// Plan region: header | expert_total[E_l] | expert_block_off[E_l+1] | expert_tile_off[E_l+1] | rank_off[R+1] |
+// seg_pool_start[E_l*R] | seg_recv_start[E_l*R] | tiles[max_tiles]
+struct PlanView {
+  PlanHeader* hdr;
+  int32_t* expert_total;
+  int32_t* expert_block_off;
+  int32_t* expert_tile_off;
+  int32_t* rank_off;
+  int32_t* seg_pool_start;
+  int32_t* seg_recv_start;
+  Tile* tiles;
+};
+
+__host__ __device__ inline int64_t align_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+__host__ __device__ inline int64_t plan_bytes(int e_local, int num_ranks, int64_t max_tiles) {
+  int64_t ints = e_local + 2 * (e_local + 1) + (num_ranks + 1) + 2 * (int64_t)e_local * num_ranks;
+  return 64 + align_up(ints * 4, 32) + max_tiles * (int64_t)sizeof(Tile);
+}
+
+__host__ __device__ inline PlanView plan_view(void* base, int e_local, int num_ranks) {
+  PlanView v;
+  char* p = static_cast<char*>(base);
+  v.hdr = reinterpret_cast<PlanHeader*>(p);
+  int32_t* q = reinterpret_cast<int32_t*>(p + 64);
+  v.expert_total = q;            q += e_local;
+  v.expert_block_off = q;        q += e_local + 1;
+  v.expert_tile_off = q;         q += e_local + 1;
+  v.rank_off = q;                q += num_ranks + 1;
+  v.seg_pool_start = q;          q += (int64_t)e_local * num_ranks;
+  v.seg_recv_start = q;          q += (int64_t)e_local * num_ranks;
+  int64_t ints = q - reinterpret_cast<int32_t*>(p + 64);
+  v.tiles = reinterpret_cast<Tile*>(p + 64 + align_up(ints * 4, 32));
+  return v;
+}
+
+// Row of a 128-row scale chunk that holds token row i of the chunk: the layout `tcgen05.cp.32x128b.warpx4` expects
+// (lane i%32 receives the four 32-row groups side by side).
+__host__ __device__ inline int chunk_pos(int i) { return (i & 31) * 4 + ((i >> 5) & 3); }
+
+// Device status words (int32[8]): [0] != 0 means a bounded wait expired; [1] kernel id, [2] role, [3] block,
+// [4] bad-argument counter (e.g. an expert id out of range seen by the dispatch).
+enum { kStatusTimeout = 0, kStatusKernel = 1, kStatusRole = 2, kStatusBlock = 3, kStatusBadIndex = 4 };
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------------------------
+// number formats
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(v, __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float e2m1_to_float(uint32_t nib) {
+  // 0, .5, 1, 1.5, 2, 3, 4, 6 with the sign in bit 3
+  const uint32_t mag = nib & 7u;
+  float v = mag < 4u ? 0.5f * mag : (mag == 4u ? 2.f : (mag == 5u ? 3.f : (mag == 6u ? 4.f : 6.f)));
+  return (nib & 8u) ? -v : v;
+}
+
+__device__ __forceinline__ float ue8m0_to_float(uint32_t b) { return __uint_as_float(b << 23); }
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// ---------------------------------------------------------------------------------------------------------------
+// L1 epilogue for one (token, channel): BF16 rounding of both accumulators, clamp (upper only for the gate),
+// sigmoid, (gate*sig)*up*weight.  Operation order and roundings follow the reference's epilogue
+// (backend/kernel/epilogue.py:190-221).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float swiglu_act(float gate_acc, float up_acc, float weight, float clamp, bool fast_math) {
+  float g = bf16_round(gate_acc);
+  float u = bf16_round(up_acc);
+  g = fminf(g, clamp);                       // clamp is a BF16-representable value (or +inf)
+  u = fminf(fmaxf(u, -clamp), clamp);
+  float gated;
+  if (fast_math) {
+    float e, r;
+    const float t = __fmul_rn(-g, 1.4426950408889634f);
+    asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(t));
+    const float d = __fadd_rn(1.0f, e);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    gated = __fmul_rn(g, r);
+  } else {
+    gated = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+  }
+  return __fmul_rn(__fmul_rn(gated, u), weight);
+}
+
+// UE8M0 exponent of a non-negative amax by the integer-carry method (backend/kernel/ptx_g.py:235-241).
+__device__ __forceinline__ int ue8m0_exp_of_amax(float amax) {
+  const uint32_t bits = __float_as_uint(amax);
+  const int rounded = static_cast<int>((bits + (0x7FFFFFu - (0x60u << 16))) >> 23);
+  return max(rounded, 105 + 8) - 8;
+}
+
+__device__ __forceinline__ float ue8m0_inv(int sf_exp) { return __uint_as_float(static_cast<uint32_t>(254 - sf_exp) << 23); }
+
+// max over the warp of non-negative floats (IEEE bits of non-negative floats order like unsigned integers)
+__device__ __forceinline__ float warp_max_nonneg(float v) {
+  return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
+}
+
+__device__ __forceinline__ void report_bad_index(int32_t* status) { atomicAdd(&status[kStatusBadIndex], 1); }
+#endif  // __CUDACC__
+
+// kernels and launchers implemented in the .cu files ------------------------------------------------------------------
+struct Ctx {             // resolved pointers of one call
+  MmoeGeometry geo;
+  MmoeLayout lay;
+  char* ws;
+  int e_local;
+  int kmax;              // min(k, E/R)
+  template <typename T> T* at(int64_t off) const { return reinterpret_cast<T*>(ws + off); }
+};
+
+cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int ids64, const float* w,
+                         const uint8_t* pad, int m, int shared_bm, cudaStream_t s);
+cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s);
+cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s);
+cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
+cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s);
+cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
+cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
+int prepare_umma(const MmoeGeometry& geo);   // returns an MMOE_* code
+
+}  // namespace mmoe

@@ -1,0 +1,602 @@
+// HBM-bound support kernels of the MegaMoE layer for sm_100a: input quantiser, route ordering, pool plan and
+// placement, top-k combine.  All integer work here is deterministic (no order-dependent atomics), so the dispatch
+// layout is reproducible run to run.
+#include <algorithm>
+
+#include "mmoe_common.cuh"
+
+namespace mmoe {
+
+// =====================================================================================================================
+// Kernel (a): BF16 -> MXFP8 E4M3 with one UE8M0 scale per 32 elements, four scale bytes per int32 word.
+// Follows the reference quantiser (backend/staging.py:36-82): scale = 2^ceil(log2(max(amax, 1e-4) / 448)), exponent
+// clamped to [1, 254]; values multiplied by the exact reciprocal and rounded to nearest even.
+// One thread converts 8 elements (one 16-byte load, one 8-byte store); 4 threads share a scale, 16 a scale word.
+// =====================================================================================================================
+__global__ void __launch_bounds__(256) stage_kernel(
+    const uint4* __restrict__ hidden, uint2* __restrict__ x_q, int32_t* __restrict__ x_sf,
+    int32_t* __restrict__ shared_sf, int64_t shared_rows, int shared_bm,
+    const void* __restrict__ ids_in, int ids64, const float* __restrict__ w_in, const uint8_t* __restrict__ pad,
+    int64_t* __restrict__ ids_out, float* __restrict__ w_out, int m, int h, int k) {
+  const int vec_per_row = h / 8;
+  const int64_t total = (int64_t)m * vec_per_row;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total_padded = (total + 31) / 32 * 32;   // whole warps iterate together (shuffles below)
+  for (int64_t i = tid; i < total_padded; i += stride) {
+    const bool live = i < total;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = hidden[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float v[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(p[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, 1e-4f);
+    const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
+    int e = static_cast<int>((bits >> 23) & 0xFFu) + ((bits & 0x7FFFFFu) != 0u);
+    e = min(max(e, 1), 254);
+    const float inv = __fdiv_rn(1.0f, __uint_as_float(static_cast<uint32_t>(e) << 23));
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= static_cast<uint32_t>(float_to_e4m3(__fmul_rn(v[j], inv))) << (8 * j);
+      hi |= static_cast<uint32_t>(float_to_e4m3(__fmul_rn(v[4 + j], inv))) << (8 * j);
+    }
+    if (live) x_q[i] = make_uint2(lo, hi);
+    // scale word: lanes 0,4,8,12 of each 16-lane group hold the four exponents
+    const int lane = threadIdx.x & 31;
+    const int base = lane & 16;
+    uint32_t word = static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 0));
+    word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 4)) << 8;
+    word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 8)) << 16;
+    word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 12)) << 24;
+    if (live && (lane & 15) == 0) {
+      const int64_t t = i / vec_per_row;
+      const int w = static_cast<int>(i % vec_per_row) / 16;
+      x_sf[t * (h / kTileK) + w] = static_cast<int32_t>(word);
+      if (shared_bm > 0) {
+        // row of token t in the BLOCK_M-dependent shared-expert scale layout (backend/staging.py:85-95)
+        const int64_t mm = t % shared_bm;
+        const int64_t bm_al = (shared_bm + 127) / 128 * 128;
+        const int64_t row = (t / shared_bm) * bm_al + (mm / 128) * 128 + (mm % 32) * 4 + (mm % 128) / 32;
+        shared_sf[(int64_t)w * shared_rows + row] = static_cast<int32_t>(word);
+      }
+    }
+  }
+  // routing repack (backend/staging.py:244-251)
+  const int64_t routes = (int64_t)m * k;
+  for (int64_t r = tid; r < routes; r += stride) {
+    const int64_t t = r / k;
+    const bool is_pad = pad != nullptr && pad[t] != 0;
+    const int64_t id = ids64 ? static_cast<const int64_t*>(ids_in)[r] : static_cast<const int32_t*>(ids_in)[r];
+    ids_out[r] = is_pad ? -1 : id;
+    w_out[r] = is_pad ? 0.f : w_in[r];
+  }
+}
+
+cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int ids64, const float* w,
+                         const uint8_t* pad, int m, int shared_bm, cudaStream_t s) {
+  if (m == 0) return cudaSuccess;
+  const int h = c.geo.hidden;
+  const int64_t total = (int64_t)m * h / 8;
+  int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  stage_kernel<<<blocks, 256, 0, s>>>(
+      static_cast<const uint4*>(hidden), c.at<uint2>(c.lay.x), c.at<int32_t>(c.lay.x_sf),
+      c.at<int32_t>(c.lay.shared_x_sf), c.lay.shared_sf_rows, c.geo.num_shared_experts > 0 ? shared_bm : 0, ids, ids64, w,
+      pad, c.at<int64_t>(c.lay.topk_idx), c.at<float>(c.lay.topk_weights), m, h, c.geo.num_topk);
+  return cudaGetLastError();
+}
+
+// =====================================================================================================================
+// Route ordering: a stable counting sort of the routes (token*k + slot) by destination expert in three passes over
+// chunks of 128 tokens.  Replaces the atomics-ordered slot assignment of the reference (backend/kernel/dispatch.py:
+// 348-410) with a deterministic order; the per-expert counts are the same numbers.
+// =====================================================================================================================
+constexpr int kSortThreads = 256;
+constexpr int kMaxChunkRoutes = kSortChunkTokens * 32;
+
+// pass A: per chunk, local rank of every route among the chunk's routes to the same expert + per-chunk expert counts
+__global__ void __launch_bounds__(kSortThreads) sort_local_kernel(
+    const int64_t* __restrict__ topk_idx, int32_t* __restrict__ route_pos, int32_t* __restrict__ chunk_count,
+    int32_t* __restrict__ status, int m, int k, int num_experts) {
+  extern __shared__ int32_t sm[];
+  int32_t* ids = sm;                       // [chunk routes]
+  int32_t* hist = sm + kSortChunkTokens * k;   // [num_experts]
+  const int chunk = blockIdx.x;
+  const int r0 = chunk * kSortChunkTokens * k;
+  const int n = min(kSortChunkTokens * k, m * k - r0);
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int64_t id = topk_idx[r0 + i];
+    if (id >= num_experts) { report_bad_index(status); id = -1; }
+    ids[i] = id < 0 ? -1 : static_cast<int32_t>(id);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    int rank = -1;
+    if (e >= 0) {
+      rank = 0;
+      for (int j = 0; j < i; ++j) rank += (ids[j] == e);
+      atomicAdd(&hist[e], 1);             // a count, not an order: deterministic
+    }
+    route_pos[r0 + i] = rank;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) chunk_count[(int64_t)chunk * num_experts + e] = hist[e];
+}
+
+// pass B: one block; per expert an exclusive scan over chunks, then an exclusive scan over experts
+__global__ void __launch_bounds__(1024) sort_scan_kernel(
+    int32_t* __restrict__ chunk_count, int32_t* __restrict__ send_count, int32_t* __restrict__ send_offset,
+    int32_t* __restrict__ recv_count_if_single, int num_chunks, int num_experts) {
+  __shared__ int32_t totals[2048 + 1];
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int v = chunk_count[(int64_t)c * num_experts + e];
+      chunk_count[(int64_t)c * num_experts + e] = run;
+      run += v;
+    }
+    totals[e] = run;
+    send_count[e] = run;
+    if (recv_count_if_single != nullptr) recv_count_if_single[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      send_offset[e] = run;
+      run += totals[e];
+    }
+    send_offset[num_experts] = run;
+  }
+}
+
+// pass C: final position of every route, and the inverse map
+__global__ void __launch_bounds__(kSortThreads) sort_place_kernel(
+    const int64_t* __restrict__ topk_idx, const int32_t* __restrict__ chunk_base,
+    const int32_t* __restrict__ send_offset, int32_t* __restrict__ route_pos, int32_t* __restrict__ sorted_route,
+    int m, int k, int num_experts) {
+  const int64_t total = (int64_t)m * k;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < total; r += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t id = topk_idx[r];
+    int pos = -1;
+    if (id >= 0 && id < num_experts) {
+      const int chunk = static_cast<int>(r / (kSortChunkTokens * k));
+      pos = send_offset[id] + chunk_base[(int64_t)chunk * num_experts + id] + route_pos[r];
+      sorted_route[pos] = static_cast<int32_t>(r);
+    }
+    route_pos[r] = pos;
+  }
+}
+
+cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s) {
+  const int k = c.geo.num_topk, e = c.geo.num_experts;
+  const int chunks = max(1, (m + kSortChunkTokens - 1) / kSortChunkTokens);
+  int32_t* chunk_count = c.at<int32_t>(c.lay.sort_scratch);
+  const size_t smem = (size_t)(kSortChunkTokens * k + e) * sizeof(int32_t);
+  sort_local_kernel<<<chunks, kSortThreads, smem, s>>>(c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos),
+                                                       chunk_count, c.at<int32_t>(c.lay.status), m, k, e);
+  sort_scan_kernel<<<1, 1024, 0, s>>>(chunk_count, c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset),
+                                      c.geo.num_ranks == 1 ? c.at<int32_t>(c.lay.recv_count) : nullptr, chunks, e);
+  if (m > 0) {
+    const int blocks = static_cast<int>(std::min<int64_t>(((int64_t)m * k + kSortThreads - 1) / kSortThreads, 148 * 8));
+    sort_place_kernel<<<blocks, kSortThreads, 0, s>>>(c.at<int64_t>(c.lay.topk_idx), chunk_count,
+                                                      c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.route_pos),
+                                                      c.at<int32_t>(c.lay.sorted_route), m, k, e);
+  }
+  return cudaGetLastError();
+}
+
+// =====================================================================================================================
+// EP > 1: gather the rows, scale words and weights of this rank's routes into send order (sorted by destination
+// expert, hence by destination rank), ready for the all-to-allv.
+// =====================================================================================================================
+__global__ void __launch_bounds__(256) pack_kernel(
+    const uint4* __restrict__ x, const int32_t* __restrict__ x_sf, const float* __restrict__ topk_w,
+    const int32_t* __restrict__ sorted_route, const int32_t* __restrict__ send_offset, uint4* __restrict__ send_x,
+    int32_t* __restrict__ send_sf, float* __restrict__ send_w, int h, int k, int num_experts) {
+  const int total = send_offset[num_experts];
+  const int vec = h / 16, words = h / kTileK;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int p = warp; p < total; p += nwarps) {
+    const int route = sorted_route[p];
+    const int t = route / k;
+    for (int v = lane; v < vec; v += 32) send_x[(int64_t)p * vec + v] = x[(int64_t)t * vec + v];
+    for (int w = lane; w < words; w += 32) send_sf[(int64_t)p * words + w] = x_sf[(int64_t)t * words + w];
+    if (lane == 0) send_w[p] = topk_w[route];
+  }
+}
+
+cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s) {
+  if (m == 0) return cudaSuccess;
+  pack_kernel<<<148 * 4, 256, 0, s>>>(c.at<uint4>(c.lay.x), c.at<int32_t>(c.lay.x_sf), c.at<float>(c.lay.topk_weights),
+                                      c.at<int32_t>(c.lay.sorted_route), c.at<int32_t>(c.lay.send_offset),
+                                      c.at<uint4>(c.lay.send_x), c.at<int32_t>(c.lay.send_sf), c.at<float>(c.lay.send_w),
+                                      c.geo.hidden, c.geo.num_topk, c.geo.num_experts);
+  return cudaGetLastError();
+}
+
+// =====================================================================================================================
+// Pool plan (one block).  Pool order: local experts ascending, each expert starting on a BLOCK_M boundary
+// (backend/kernel/dispatch.py:431-447); inside an expert, source ranks ascending and each source's routes in its send
+// order (token, slot) -- a fixed order where the reference's is arrival order.
+// =====================================================================================================================
+__device__ __forceinline__ int tiles_of_rows(int rows_in_chunk) {
+  return rows_in_chunk <= 0 ? 0 : (rows_in_chunk > kMaxTileTokens ? 2 : 1);
+}
+
+__device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int first_block, bool write) {
+  // tokens [0, n) of one expert laid out in blocks of block_m rows starting at pool block `first_block`
+  const int chunks_per_block = (block_m + kChunkRows - 1) / kChunkRows;
+  int count = 0;
+  for (int b = 0; b * block_m < n; ++b) {
+    const int in_block = min(block_m, n - b * block_m);
+    for (int s = 0; s < chunks_per_block; ++s) {
+      const int rows = min(kChunkRows, in_block - s * kChunkRows);
+      if (rows <= 0) break;
+      const int row0 = row_base + b * block_m + s * kChunkRows;
+      const int chunk = (first_block + b) * chunks_per_block + s;
+      if (rows > kMaxTileTokens) {
+        if (write) {
+          out[count] = Tile{expert, row0, 64, chunk, 0, {0, 0, 0}};
+          out[count + 1] = Tile{expert, row0 + 64, rows - 64, chunk, 2, {0, 0, 0}};
+        }
+        count += 2;
+      } else {
+        if (write) out[count] = Tile{expert, row0, rows, chunk, 0, {0, 0, 0}};
+        count += 1;
+      }
+    }
+  }
+  return count;
+}
+
+__global__ void __launch_bounds__(1024) plan_kernel(
+    char* __restrict__ plan_base, const int32_t* __restrict__ recv_count, int32_t* __restrict__ stats, int e_local,
+    int num_ranks, int block_m, int m, int has_shared) {
+  PlanView pv = plan_view(plan_base, e_local, num_ranks);
+  __shared__ int32_t s_blocks[513], s_tiles[513];
+  // per-source totals -> rank offsets in receive order
+  if (threadIdx.x <= num_ranks) {
+    // rank_off[r] = sum over sources < r of all their routes to this rank
+    int run = 0;
+    for (int r = 0; r < (int)threadIdx.x; ++r)
+      for (int e = 0; e < e_local; ++e) run += recv_count[r * e_local + e];
+    pv.rank_off[threadIdx.x] = run;
+    if ((int)threadIdx.x == num_ranks) pv.hdr->total_recv = run;
+  }
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) {
+    int tot = 0;
+    for (int r = 0; r < num_ranks; ++r) tot += recv_count[r * e_local + e];
+    pv.expert_total[e] = tot;
+    s_blocks[e] = (tot + block_m - 1) / block_m;
+    s_tiles[e] = emit_tiles(nullptr, e, 0, tot, block_m, 0, false);
+    if (stats != nullptr) stats[e] += tot;      // cumulative per-expert receive statistics (dispatch.py:644-650)
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rb = 0, rt = 0;
+    for (int e = 0; e < e_local; ++e) {
+      pv.expert_block_off[e] = rb;
+      pv.expert_tile_off[e] = rt;
+      rb += s_blocks[e];
+      rt += s_tiles[e];
+    }
+    pv.expert_block_off[e_local] = rb;
+    pv.expert_tile_off[e_local] = rt;
+    pv.hdr->num_routed_tiles = rt;
+    pv.hdr->num_pool_blocks = rb;
+    pv.hdr->block_m = block_m;
+    pv.hdr->num_tokens = m;
+    // shared-expert tiles: the call's own tokens in blocks of block_m (chunk numbering of backend/staging.py:85-95)
+    int ns = 0;
+    if (has_shared) ns = emit_tiles(pv.tiles + rt, kSharedExpert, 0, m, block_m, 0, true);
+    pv.hdr->num_shared_tiles = ns;
+  }
+  __syncthreads();
+  // per-source cumulative offsets over experts in receive order (one thread per source rank)
+  if ((int)threadIdx.x < num_ranks) {
+    const int r = threadIdx.x;
+    int run = pv.rank_off[r];
+    for (int e = 0; e < e_local; ++e) {
+      pv.seg_recv_start[e * num_ranks + r] = run;
+      run += recv_count[r * e_local + e];
+    }
+  }
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) {
+    int run = pv.expert_block_off[e] * block_m;
+    for (int r = 0; r < num_ranks; ++r) {
+      pv.seg_pool_start[e * num_ranks + r] = run;
+      run += recv_count[r * e_local + e];
+    }
+    emit_tiles(pv.tiles + pv.expert_tile_off[e], e, pv.expert_block_off[e] * block_m, pv.expert_total[e], block_m,
+               pv.expert_block_off[e], true);
+  }
+}
+
+// Place: one warp per pool row of every routed tile: copy the FP8 row, scatter its scale words into the chunk layout,
+// record the top-k weight and the receive-order row that takes the expert output.
+__global__ void __launch_bounds__(256) place_kernel(
+    char* __restrict__ plan_base, const uint4* __restrict__ src_x, const int32_t* __restrict__ src_sf,
+    const float* __restrict__ src_w, const int32_t* __restrict__ sorted_route, uint4* __restrict__ pool_x,
+    int32_t* __restrict__ pool_sf, float* __restrict__ pool_w, int32_t* __restrict__ pool_dst, int64_t pool_sf_rows,
+    int e_local, int num_ranks, int h, int k, int direct) {
+  PlanView pv = plan_view(plan_base, e_local, num_ranks);
+  const int ntiles = pv.hdr->num_routed_tiles;
+  const int block_m = pv.hdr->block_m;
+  const int vec = h / 16, words = h / kTileK;
+  const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const Tile tile = pv.tiles[t];
+    const int e = tile.expert;
+    const int expert_row0 = pv.expert_block_off[e] * block_m;
+    for (int i = warp_in_block; i < tile.n_valid; i += warps) {
+      const int p = tile.row0 + i;
+      const int j = p - expert_row0;           // index of this row among the expert's routes
+      int r = 0, acc = 0;
+      for (; r < num_ranks - 1; ++r) {          // source rank that owns the j-th route
+        const int next = pv.seg_pool_start[e * num_ranks + r + 1] - expert_row0;
+        if (j < next) break;
+      }
+      acc = pv.seg_pool_start[e * num_ranks + r] - expert_row0;
+      const int recv_row = pv.seg_recv_start[e * num_ranks + r] + (j - acc);
+      int64_t src_row = recv_row;
+      float w;
+      if (direct) {                              // EP1: read the staged inputs in place
+        const int route = sorted_route[recv_row];
+        src_row = route / k;
+        w = src_w[route];
+      } else {
+        w = src_w[recv_row];
+      }
+      for (int v = lane; v < vec; v += 32) pool_x[(int64_t)p * vec + v] = src_x[src_row * vec + v];
+      const int pos = tile.sf_chunk * kChunkRows + chunk_pos(tile.sf_col * 32 + i);
+      for (int wd = lane; wd < words; wd += 32) pool_sf[(int64_t)wd * pool_sf_rows + pos] = src_sf[src_row * words + wd];
+      if (lane == 0) {
+        pool_w[p] = w;
+        pool_dst[p] = recv_row;
+      }
+    }
+  }
+}
+
+cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {
+  const int R = c.geo.num_ranks;
+  plan_kernel<<<1, 1024, 0, s>>>(c.ws + c.lay.plan, c.at<int32_t>(c.lay.recv_count), stats, c.e_local, R, block_m, m,
+                                 c.geo.num_shared_experts > 0);
+  const bool direct = R == 1;
+  place_kernel<<<148 * 4, 256, 0, s>>>(
+      c.ws + c.lay.plan, direct ? c.at<uint4>(c.lay.x) : c.at<uint4>(c.lay.recv_x),
+      direct ? c.at<int32_t>(c.lay.x_sf) : c.at<int32_t>(c.lay.recv_sf),
+      direct ? c.at<float>(c.lay.topk_weights) : c.at<float>(c.lay.recv_w), c.at<int32_t>(c.lay.sorted_route),
+      c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf), c.at<float>(c.lay.pool_w), c.at<int32_t>(c.lay.pool_dst),
+      c.lay.pool_sf_rows, c.e_local, R, c.geo.hidden, c.geo.num_topk, direct ? 1 : 0);
+  return cudaGetLastError();
+}
+
+// =====================================================================================================================
+// Combine: y[t] = bf16_rn(sum of the token's valid slots in ascending slot order, shared expert last), sequential FP32
+// additions starting from zero (backend/kernel/combine.py:128-199).  One thread owns 8 consecutive output elements.
+// =====================================================================================================================
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(p[j]);
+    acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
+    acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+  }
+}
+
+__global__ void __launch_bounds__(256) combine_kernel(
+    const uint4* __restrict__ rows, const int32_t* __restrict__ route_pos, const uint4* __restrict__ shared_out,
+    uint4* __restrict__ y, int m, int h, int k) {
+  const int vec = h / 8;
+  const int64_t total = (int64_t)m * vec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / vec;
+    const int v = static_cast<int>(i % vec);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < k; ++s) {
+      const int pos = route_pos[t * k + s];
+      if (pos >= 0) add_bf16x8(acc, rows[(int64_t)pos * vec + v]);
+    }
+    if (shared_out != nullptr) add_bf16x8(acc, shared_out[i]);
+    uint4 out;
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    y[i] = out;
+  }
+}
+
+cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s) {
+  if (m == 0) return cudaSuccess;
+  const int64_t total = (int64_t)m * c.geo.hidden / 8;
+  const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  const uint4* rows = c.geo.num_ranks == 1 ? c.at<uint4>(c.lay.ret) : c.at<uint4>(c.lay.ret_recv);
+  combine_kernel<<<blocks, 256, 0, s>>>(rows, c.at<int32_t>(c.lay.route_pos),
+                                        c.geo.num_shared_experts > 0 ? c.at<uint4>(c.lay.shared_out) : nullptr,
+                                        static_cast<uint4*>(y), m, c.geo.hidden, c.geo.num_topk);
+  return cudaGetLastError();
+}
+
+// =====================================================================================================================
+// Scalar validation engine (tests only): the same plan, pool, epilogues and output addressing as the tensor-core
+// kernels, with the two block-scaled GEMMs written as plain FP32 dot products.  One warp = one 32-channel scale group.
+// =====================================================================================================================
+template <bool kFp8Weights>
+__device__ __forceinline__ float dot_group(const uint8_t* __restrict__ xrow, const uint8_t* __restrict__ wrow) {
+  // 32 K elements: xrow -> 32 e4m3 bytes; wrow -> 16 packed bytes (FP4) or 32 e4m3 bytes
+  float acc = 0.f;
+  if (kFp8Weights) {
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j) acc = fmaf(e4m3_to_float(xrow[j]), e4m3_to_float(wrow[j]), acc);
+  } else {
+#pragma unroll 8
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t b = wrow[j];
+      acc = fmaf(e4m3_to_float(xrow[2 * j]), e2m1_to_float(b & 15u), acc);
+      acc = fmaf(e4m3_to_float(xrow[2 * j + 1]), e2m1_to_float(b >> 4), acc);
+    }
+  }
+  return acc;
+}
+
+// scale byte of weight row `row` (within its matrix of n_rows rows), K group g, in the 4x32-transposed MN-major layout
+__device__ __forceinline__ uint32_t weight_sf_byte(const int32_t* __restrict__ sf, int n_rows, int row, int g) {
+  const int blk = row / 128, in = row % 128;
+  const int pos = blk * 128 + chunk_pos(in);
+  const uint32_t word = static_cast<uint32_t>(sf[(int64_t)(g / 4) * n_rows + pos]);
+  return (word >> (8 * (g % 4))) & 0xFFu;
+}
+
+__device__ __forceinline__ uint32_t token_sf_byte(const int32_t* __restrict__ sf, int64_t sf_rows, const Tile& tile,
+                                                  int i, int g) {
+  const int pos = tile.sf_chunk * kChunkRows + chunk_pos(tile.sf_col * 32 + i);
+  const uint32_t word = static_cast<uint32_t>(sf[(int64_t)(g / 4) * sf_rows + pos]);
+  return (word >> (8 * (g % 4))) & 0xFFu;
+}
+
+// address of weight row `row` (0..rows_per_expert) of expert e, for plain and two-slice weight tensors
+__device__ __forceinline__ const uint8_t* weight_row_ptr(const uint8_t* base, int e, int row, int rows_per_expert,
+                                                         int64_t row_bytes, int64_t slice_stride) {
+  if (slice_stride > 0) {
+    const int half = rows_per_expert / 2;
+    return base + (row / half) * slice_stride + ((int64_t)e * half + row % half) * row_bytes;
+  }
+  return base + ((int64_t)e * rows_per_expert + row) * row_bytes;
+}
+
+__global__ void __launch_bounds__(128) simt_l1_kernel(
+    char* __restrict__ plan_base, int e_local, int num_ranks, int first_tile, int num_tiles_from_hdr_shared,
+    const uint8_t* __restrict__ tok_x, const int32_t* __restrict__ tok_sf, int64_t tok_sf_rows,
+    const float* __restrict__ tok_w, const uint8_t* __restrict__ w13, const int32_t* __restrict__ w13_sf,
+    uint8_t* __restrict__ act_x, uint8_t* __restrict__ act_sf, int64_t act_sf_rows, int h, int inter, float clamp,
+    int fast_math, int fp8_weights, int64_t slice_stride) {
+  PlanView pv = plan_view(plan_base, e_local, num_ranks);
+  const int ntiles = num_tiles_from_hdr_shared ? pv.hdr->num_shared_tiles : pv.hdr->num_routed_tiles;
+  const int base = num_tiles_from_hdr_shared ? pv.hdr->num_routed_tiles : 0;
+  const int groups = inter / 32;
+  const int lane = threadIdx.x & 31;
+  const int64_t work = (int64_t)ntiles * groups;
+  const int64_t wstride = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t wi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wi < work; wi += wstride) {
+    const Tile tile = pv.tiles[base + wi / groups];
+    const int g_out = static_cast<int>(wi % groups);
+    const int c = g_out * 32 + lane;
+    const bool shared = tile.expert == kSharedExpert;
+    const int e = shared ? 0 : tile.expert;
+    const int64_t wrow_bytes = fp8_weights ? h : h / 2;
+    const uint8_t* wg = weight_row_ptr(w13, e, c, 2 * inter, wrow_bytes, slice_stride);
+    const uint8_t* wu = weight_row_ptr(w13, e, inter + c, 2 * inter, wrow_bytes, slice_stride);
+    const int32_t* wsf = w13_sf + (int64_t)e * (h / 128) * 2 * inter;
+    for (int i = 0; i < tile.n_valid; ++i) {
+      const uint8_t* xr = tok_x + (int64_t)(tile.row0 + i) * h;
+      float accg = 0.f, accu = 0.f;
+      for (int g = 0; g < h / 32; ++g) {
+        const float sx = ue8m0_to_float(token_sf_byte(tok_sf, tok_sf_rows, tile, i, g));
+        const float sg = ue8m0_to_float(weight_sf_byte(wsf, 2 * inter, c, g));
+        const float su = ue8m0_to_float(weight_sf_byte(wsf, 2 * inter, inter + c, g));
+        float dg, du;
+        if (fp8_weights) {
+          dg = dot_group<true>(xr + g * 32, wg + g * 32);
+          du = dot_group<true>(xr + g * 32, wu + g * 32);
+        } else {
+          dg = dot_group<false>(xr + g * 32, wg + g * 16);
+          du = dot_group<false>(xr + g * 32, wu + g * 16);
+        }
+        accg = fmaf(dg, sx * sg, accg);
+        accu = fmaf(du, sx * su, accu);
+      }
+      const float wt = shared ? 1.0f : tok_w[tile.row0 + i];
+      const float act = swiglu_act(accg, accu, wt, clamp, fast_math != 0);
+      const float amax = warp_max_nonneg(fabsf(act));
+      const int sf_exp = ue8m0_exp_of_amax(amax);
+      act_x[(int64_t)(tile.row0 + i) * inter + c] = float_to_e4m3(__fmul_rn(act, ue8m0_inv(sf_exp)));
+      if (lane == 0) {
+        const int pos = tile.sf_chunk * kChunkRows + chunk_pos(tile.sf_col * 32 + i);
+        act_sf[((int64_t)(g_out / 4) * act_sf_rows + pos) * 4 + (g_out % 4)] = static_cast<uint8_t>(sf_exp);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) simt_l2_kernel(
+    char* __restrict__ plan_base, int e_local, int num_ranks, int use_shared_tiles,
+    const uint8_t* __restrict__ act_x, const int32_t* __restrict__ act_sf, int64_t act_sf_rows,
+    const uint8_t* __restrict__ w2, const int32_t* __restrict__ w2_sf, const int32_t* __restrict__ pool_dst,
+    __nv_bfloat16* __restrict__ out, int h, int inter, int fp8_weights, int64_t slice_stride) {
+  PlanView pv = plan_view(plan_base, e_local, num_ranks);
+  const int ntiles = use_shared_tiles ? pv.hdr->num_shared_tiles : pv.hdr->num_routed_tiles;
+  const int base = use_shared_tiles ? pv.hdr->num_routed_tiles : 0;
+  const int groups = h / 32;
+  const int lane = threadIdx.x & 31;
+  const int64_t work = (int64_t)ntiles * groups;
+  const int64_t wstride = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t wi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wi < work; wi += wstride) {
+    const Tile tile = pv.tiles[base + wi / groups];
+    const int row = static_cast<int>(wi % groups) * 32 + lane;   // output feature
+    const bool shared = tile.expert == kSharedExpert;
+    const int e = shared ? 0 : tile.expert;
+    const int64_t wrow_bytes = fp8_weights ? inter : inter / 2;
+    const uint8_t* wr = weight_row_ptr(w2, e, row, h, wrow_bytes, slice_stride);
+    const int32_t* wsf = w2_sf + (int64_t)e * (inter / 128) * h;
+    for (int i = 0; i < tile.n_valid; ++i) {
+      const uint8_t* xr = act_x + (int64_t)(tile.row0 + i) * inter;
+      float acc = 0.f;
+      for (int g = 0; g < inter / 32; ++g) {
+        const float sx = ue8m0_to_float(token_sf_byte(act_sf, act_sf_rows, tile, i, g));
+        const float sw = ue8m0_to_float(weight_sf_byte(wsf, h, row, g));
+        const float d = fp8_weights ? dot_group<true>(xr + g * 32, wr + g * 32) : dot_group<false>(xr + g * 32, wr + g * 16);
+        acc = fmaf(d, sx * sw, acc);
+      }
+      const int64_t dst = shared ? (tile.row0 + i) : pool_dst[tile.row0 + i];
+      out[dst * h + row] = __float2bfloat16_rn(acc);
+    }
+  }
+}
+
+cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m,
+                                cudaStream_t s) {
+  const int h = c.geo.hidden, inter = c.geo.intermediate;
+  const int blocks = 148 * 8;
+  char* plan = c.ws + c.lay.plan;
+  simt_l1_kernel<<<blocks, 128, 0, s>>>(plan, c.e_local, c.geo.num_ranks, 0, 0, c.at<uint8_t>(c.lay.pool_x),
+                                        c.at<int32_t>(c.lay.pool_sf), c.lay.pool_sf_rows, c.at<float>(c.lay.pool_w),
+                                        static_cast<const uint8_t*>(w.w13), static_cast<const int32_t*>(w.w13_sf),
+                                        c.at<uint8_t>(c.lay.act_x), c.at<uint8_t>(c.lay.act_sf), c.lay.pool_sf_rows, h,
+                                        inter, o.activation_clamp, o.fast_math, 0, w.w13_slice_stride);
+  simt_l2_kernel<<<blocks, 128, 0, s>>>(plan, c.e_local, c.geo.num_ranks, 0, c.at<uint8_t>(c.lay.act_x),
+                                        c.at<int32_t>(c.lay.act_sf), c.lay.pool_sf_rows,
+                                        static_cast<const uint8_t*>(w.w2), static_cast<const int32_t*>(w.w2_sf),
+                                        c.at<int32_t>(c.lay.pool_dst), c.at<__nv_bfloat16>(c.lay.ret), h, inter, 0,
+                                        w.w2_slice_stride);
+  if (c.geo.num_shared_experts > 0 && m > 0) {
+    simt_l1_kernel<<<blocks, 128, 0, s>>>(plan, c.e_local, c.geo.num_ranks, 0, 1, c.at<uint8_t>(c.lay.x),
+                                          c.at<int32_t>(c.lay.shared_x_sf), c.lay.shared_sf_rows, nullptr,
+                                          static_cast<const uint8_t*>(w.shared_w13),
+                                          static_cast<const int32_t*>(w.shared_w13_sf),
+                                          c.at<uint8_t>(c.lay.shared_act_x), c.at<uint8_t>(c.lay.shared_act_sf),
+                                          c.lay.shared_sf_rows, h, inter, o.activation_clamp, o.fast_math, 1, 0);
+    simt_l2_kernel<<<blocks, 128, 0, s>>>(plan, c.e_local, c.geo.num_ranks, 1, c.at<uint8_t>(c.lay.shared_act_x),
+                                          c.at<int32_t>(c.lay.shared_act_sf), c.lay.shared_sf_rows,
+                                          static_cast<const uint8_t*>(w.shared_w2),
+                                          static_cast<const int32_t*>(w.shared_w2_sf), nullptr,
+                                          c.at<__nv_bfloat16>(c.lay.shared_out), h, inter, 1, 0);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace mmoe

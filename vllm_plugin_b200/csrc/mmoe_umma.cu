@@ -1,0 +1,588 @@
+// Grouped block-scaled GEMMs of the MegaMoE layer on the sm_100a tensor cores.
+//
+//   layer 1:  acc[ch, tok] = sum_k W13[e][ch, k] * x[tok, k]   (gate rows and up rows of one 128-channel tile in two
+//             TMEM accumulators) -> SwiGLU, x top-k weight, per-32-channel UE8M0 requantisation to E4M3
+//   layer 2:  acc[h, tok]  = sum_i W2[e][h, i] * act[tok, i]   -> BF16 rows of the return buffer
+//
+// Weights are the UMMA "A" operand (M = 128 rows), tokens the "B" operand (N = 16..112 tokens), so a small token
+// count costs a small N instead of a padded M: `tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale`, MXFP4 (E2M1) or
+// E4M3 weights x E4M3 activations with UE8M0 scales per 32 K.  The same roles exist in the reference's kernel
+// (backend/kernel/tma_warps.py, mma_warp.py, epilogue.py, scheduler.py); the structure here is B200's:
+//
+//   warp 0     producer: one thread issues the TMA tile loads (packed FP4 expands to byte containers on the way into
+//              shared memory; no cluster multicast) and 512-byte bulk copies of the scale chunks, per 128-K stage
+//   warp 1     MMA: one thread copies the scales into TMEM (tcgen05.cp) and issues 4 (x2 for layer 1) UMMAs per stage,
+//              committing each stage's shared memory back to the producer and each finished accumulator to the epilogue
+//   warps 2-5  epilogue: TMEM -> registers (thread = weight row, columns = tokens), fused math, global stores
+//
+// Persistent CTAs (one per SM) walk a static task list (tile, 128-row weight block); TMEM accumulators are double
+// buffered so the epilogue of task i overlaps the loads and MMAs of task i+1.  Every wait is bounded: when the budget
+// expires the CTA records {kernel, role, block} in the status words, lets its in-flight copies land, frees its TMEM and
+// returns; nothing traps.
+#include <cuda.h>
+
+#include "mmoe_common.cuh"
+
+namespace mmoe {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kSmemBudget = 227 * 1024 - 2048;   // dynamic shared memory we ask for at most (alignment slack excluded)
+constexpr uint32_t kTmemCols = 512;
+
+struct UmmaParams {
+  CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 128 rows
+  CUtensorMap map_w_shared;    // E4M3 weights of the shared expert
+  CUtensorMap map_tok_routed;  // E4M3 token rows (pool / activations), box 128 K x kBoxRows
+  CUtensorMap map_tok_shared;
+  const char* plan;
+  const int32_t* wsf_routed;   // [E_l][K/128][rows_per_expert] scale words, 4x32 transposed per 128 rows
+  const int32_t* wsf_shared;
+  const int32_t* tsf_routed;   // token scale chunks: word w of chunk row r at w * tsf_rows + r
+  const int32_t* tsf_shared;
+  int64_t tsf_rows_routed, tsf_rows_shared;
+  // layer-1 outputs
+  uint8_t* act_routed;
+  uint8_t* act_shared;
+  uint8_t* act_sf_routed;      // byte view of the activation scale chunks
+  uint8_t* act_sf_shared;
+  int64_t act_sf_rows_routed, act_sf_rows_shared;
+  const float* pool_w;
+  // layer-2 outputs
+  __nv_bfloat16* ret;
+  __nv_bfloat16* shared_out;
+  const int32_t* pool_dst;
+  int32_t* status;
+  int64_t timeout_ns;
+  int e_local, num_ranks;
+  int k_dim;                   // reduction length: H (layer 1) or I (layer 2)
+  int rows_per_expert;         // 2I (layer 1) or H (layer 2)
+  int routed_sliced;           // 1: routed weights are [2, E_l, rows/2, K/2] (two slices), 0: [E_l, rows, K/2]
+  int n_blocks;                // 128-row weight blocks per tile: I/128 (layer 1) or H/128 (layer 2)
+  int hidden, inter;
+  float clamp;
+  int fast_math;
+  int has_shared_weights;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ uint64_t global_timer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                       uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled, 8-row groups 1024
+// bytes apart.  Bits: [0,14) address>>4, [16,30) leading byte offset>>4 (unused here), [32,46) stride byte offset>>4,
+// [46,48) version = 1, [61,64) layout (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// Descriptor of a 512-byte scale chunk for tcgen05.cp: no swizzle, 8-row (128-byte) groups back to back.
+__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor of the block-scaled MMA: [4,6) B scale id, [7,10) A format, [10,13) B format (0 = E4M3,
+// 5 = E2M1), [15]/[16] A/B major (0 = K), [17,23) N>>3, [23] scale format (1 = UE8M0), [24,29) M>>4, [29,31) A scale id.
+__device__ __forceinline__ uint32_t make_idesc(uint32_t a_format, uint32_t n, uint32_t sf_id) {
+  return (sf_id << 4) | (a_format << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf_id << 29);
+}
+
+struct Control {          // lives at the start of shared memory
+  uint64_t full[16];
+  uint64_t empty[16];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile int32_t abort_flag;
+};
+
+struct Waiter {
+  Control* ctl;
+  int32_t* status;
+  uint64_t deadline;
+  int kernel_id, role;
+  // true when the phase completed, false when the call is being abandoned
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0;; ++spin) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((spin & 63u) == 63u) {
+        if (ctl->abort_flag != 0) return false;
+        if (global_timer() > deadline) {
+          ctl->abort_flag = 1;
+          if (atomicCAS(&status[kStatusTimeout], 0, 1) == 0) {
+            status[kStatusKernel] = kernel_id;
+            status[kStatusRole] = role;
+            status[kStatusBlock] = static_cast<int32_t>(blockIdx.x);
+          }
+          return false;
+        }
+      }
+    }
+  }
+};
+
+template <int kLayer, int kBoxRows>
+struct Shape {
+  static constexpr int kNCap = kBoxRows > kMaxTileTokens ? kMaxTileTokens : kBoxRows;   // accumulator columns per matrix
+  static constexpr int kATiles = kLayer == 1 ? 2 : 1;
+  static constexpr int kABytes = kATiles * kTileRows * kTileK;     // byte containers in shared memory
+  static constexpr int kBBytes = kBoxRows * kTileK;
+  static constexpr int kSfBytes = (kATiles + 1) * 512;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
+  static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;   // control block + stages + alignment slack
+  static constexpr int kAccCols = kATiles * kNCap;                  // TMEM columns of one accumulator stage
+  static constexpr int kSfCol = 2 * kAccCols;                       // first TMEM column of the scale region
+  static_assert(kSfCol + 4 * (kATiles + 1) <= (int)kTmemCols, "TMEM budget");
+  static_assert(kStages >= 3, "pipeline too shallow");
+};
+
+template <int kLayer, int kBoxRows>
+__global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant__ UmmaParams p) {
+  using S = Shape<kLayer, kBoxRows>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  Control* ctl = reinterpret_cast<Control*>(smem);
+  uint8_t* a_base = smem + 1024;
+  uint8_t* b_base = a_base + S::kStages * S::kABytes;
+  uint8_t* sf_base = b_base + S::kStages * S::kBBytes;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
+  const int num_routed = pv.hdr->num_routed_tiles;
+  const int num_tiles = num_routed + (p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
+  const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
+  const int k_stages = p.k_dim / kTileK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S::kStages; ++i) {
+      mbar_init(smem_u32(&ctl->full[i]), 1);
+      mbar_init(smem_u32(&ctl->empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctl->tmem_empty[i]), 128);
+    }
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  Waiter waiter{ctl, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), kLayer, warp};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
+        const Tile tile = pv.tiles[task / p.n_blocks];
+        const int nb = static_cast<int>(task % p.n_blocks);
+        const bool shared = tile.expert == kSharedExpert;
+        const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
+        const CUtensorMap* tmap = shared ? &p.map_tok_shared : &p.map_tok_routed;
+        const int e = shared ? 0 : tile.expert;
+        // weight rows of this task inside expert e: [r_a, r_a+128) and, for layer 1, the up rows [r_b, r_b+128)
+        const int r_a = nb * kTileRows, r_b = p.inter + nb * kTileRows;
+        const bool sliced = !shared && p.routed_sliced != 0;
+        const int half = p.rows_per_expert / 2;
+        const int row_a = sliced ? e * half + r_a % half : e * p.rows_per_expert + r_a;
+        const int slice_a = sliced ? r_a / half : 0;
+        const int row_b = sliced ? e * half + r_b % half : e * p.rows_per_expert + r_b;
+        const int slice_b = sliced ? r_b / half : 0;
+        const int32_t* wsf = (shared ? p.wsf_shared : p.wsf_routed) + (int64_t)e * k_stages * p.rows_per_expert;
+        const int32_t* tsf = shared ? p.tsf_shared : p.tsf_routed;
+        const int64_t tsf_rows = shared ? p.tsf_rows_shared : p.tsf_rows_routed;
+        const uint32_t a_tx = shared ? kTileRows * kTileK : kTileRows * kTileK / 2;   // packed FP4 counts its global bytes
+        const uint32_t tx = S::kATiles * a_tx + S::kBBytes + S::kSfBytes;
+        for (int kb = 0; kb < k_stages; ++kb) {
+          if (!waiter.wait(smem_u32(&ctl->empty[stage]), phase ^ 1u)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&ctl->full[stage]);
+          mbar_expect_tx(bar, tx);
+          const uint32_t a_dst = smem_u32(a_base + stage * S::kABytes);
+          const uint32_t sf_dst = smem_u32(sf_base + stage * S::kSfBytes);
+          tma_load_3d(a_dst, wmap, kb * kTileK, row_a, slice_a, bar);
+          bulk_load(sf_dst, wsf + (int64_t)kb * p.rows_per_expert + r_a, 512, bar);
+          if (kLayer == 1) {
+            tma_load_3d(a_dst + kTileRows * kTileK, wmap, kb * kTileK, row_b, slice_b, bar);
+            bulk_load(sf_dst + 512, wsf + (int64_t)kb * p.rows_per_expert + r_b, 512, bar);
+          }
+          tma_load_2d(smem_u32(b_base + stage * S::kBBytes), tmap, kb * kTileK, tile.row0, bar);
+          bulk_load(sf_dst + S::kATiles * 512, tsf + (int64_t)kb * tsf_rows + (int64_t)tile.sf_chunk * kChunkRows, 512, bar);
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
+        const Tile tile = pv.tiles[task / p.n_blocks];
+        const bool shared = tile.expert == kSharedExpert;
+        const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
+        if (!waiter.wait(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t n = static_cast<uint32_t>((tile.n_valid + 15) & ~15);
+        const uint32_t a_format = shared ? 0u : 5u;
+        const uint32_t d0 = tmem_base + acc_stage * S::kAccCols;
+        const uint32_t sf_col = tmem_base + S::kSfCol;
+        for (int kb = 0; kb < k_stages; ++kb) {
+          if (!waiter.wait(smem_u32(&ctl->full[stage]), phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(a_base + stage * S::kABytes);
+          const uint32_t b_addr = smem_u32(b_base + stage * S::kBBytes);
+          const uint32_t sf_addr = smem_u32(sf_base + stage * S::kSfBytes);
+#pragma unroll
+          for (int i = 0; i <= S::kATiles; ++i) tc_cp_sf(sf_col + 4 * i, smem_desc_sf(sf_addr + 512 * i));
+          const uint32_t sfb = sf_col + 4 * S::kATiles + tile.sf_col;
+#pragma unroll
+          for (int k = 0; k < kTileK / 32; ++k) {
+            const uint32_t idesc = make_idesc(a_format, n, k);
+            const uint64_t bdesc = smem_desc_sw128(b_addr + k * 32);
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            tc_mma(d0, smem_desc_sw128(a_addr + k * 32), bdesc, idesc, sf_col, sfb, acc);
+            if (kLayer == 1)
+              tc_mma(d0 + S::kNCap, smem_desc_sw128(a_addr + kTileRows * kTileK + k * 32), bdesc, idesc, sf_col + 4, sfb, acc);
+          }
+          tc_commit(smem_u32(&ctl->empty[stage]));      // shared memory of this stage is free once these MMAs retire
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(smem_u32(&ctl->tmem_full[acc_stage]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------------ epilogue
+    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
+      const Tile tile = pv.tiles[task / p.n_blocks];
+      const int nb = static_cast<int>(task % p.n_blocks);
+      const bool shared = tile.expert == kSharedExpert;
+      const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
+      if (!waiter.wait(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d0 = tmem_base + lane_sel + acc_stage * S::kAccCols;
+      const int n16 = (tile.n_valid + 15) & ~15;
+      const int row = nb * kTileRows + q * 32 + lane;       // channel (layer 1) or output feature (layer 2)
+      if (kLayer == 1) {
+        uint8_t* act = shared ? p.act_shared : p.act_routed;
+        uint8_t* act_sf = shared ? p.act_sf_shared : p.act_sf_routed;
+        const int64_t sf_rows = shared ? p.act_sf_rows_shared : p.act_sf_rows_routed;
+        // scale byte of (token i, channel group nb*4+q): word nb of the chunk row, byte q
+        uint8_t* sf_out = act_sf + ((int64_t)nb * sf_rows + (int64_t)tile.sf_chunk * kChunkRows) * 4 + q;
+        for (int i0 = 0; i0 < n16; i0 += 16) {
+          uint32_t g[16], u[16];
+          tc_ld16(d0 + i0, g);
+          tc_ld16(d0 + S::kNCap + i0, u);
+          tc_ld_wait();
+          int my_sf = 0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int i = i0 + j;
+            if (i < tile.n_valid) {       // uniform across the warp
+              const float wt = shared ? 1.0f : __ldg(p.pool_w + tile.row0 + i);
+              const float a = swiglu_act(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp, p.fast_math != 0);
+              const float amax = warp_max_nonneg(fabsf(a));
+              const int sf_exp = ue8m0_exp_of_amax(amax);
+              act[(int64_t)(tile.row0 + i) * p.inter + row] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
+              if (lane == j) my_sf = sf_exp;
+            }
+          }
+          if (lane < 16 && i0 + lane < tile.n_valid)
+            sf_out[chunk_pos(tile.sf_col * 32 + i0 + lane) * 4] = static_cast<uint8_t>(my_sf);
+        }
+      } else {
+        __nv_bfloat16* out = shared ? p.shared_out : p.ret;
+        for (int i0 = 0; i0 < n16; i0 += 16) {
+          uint32_t v[16];
+          tc_ld16(d0 + i0, v);
+          tc_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int i = i0 + j;
+            if (i < tile.n_valid) {
+              const int64_t dst = shared ? (int64_t)(tile.row0 + i) : (int64_t)__ldg(p.pool_dst + tile.row0 + i);
+              out[dst * p.hidden + row] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->tmem_empty[acc_stage]));
+    }
+  }
+
+  // ---------------------------------------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (ctl->abort_flag != 0) {
+    // abandoned call: give copies that are still in flight time to land in this CTA's shared memory before it exits
+    const uint64_t t0 = global_timer();
+    while (global_timer() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+int g_num_sms = 0;
+
+// token rows: 2-D map [rows, K] of E4M3 bytes
+int make_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows, uint32_t box_rows,
+             bool weights) {
+  const cuuint64_t dims[2] = {k_elems, rows};
+  const cuuint64_t strides[1] = {fp4 ? k_elems / 2 : k_elems};
+  const cuuint32_t box[2] = {kTileK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B,
+                              weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+// weights: 3-D map [slices, rows per slice, K]; a plain tensor is one slice
+int make_weight_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows_total,
+                    int64_t slice_stride) {
+  const uint64_t row_bytes = fp4 ? k_elems / 2 : k_elems;
+  const uint64_t slices = slice_stride > 0 ? 2 : 1;
+  const uint64_t rows = rows_total / slices;
+  const cuuint64_t dims[3] = {k_elems, rows, slices};
+  const cuuint64_t strides[2] = {row_bytes, slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes};
+  const cuuint32_t box[3] = {kTileK, kTileRows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+template <int kLayer, int kBoxRows>
+cudaError_t prepare_one() {
+  return cudaFuncSetAttribute(umma_kernel<kLayer, kBoxRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Shape<kLayer, kBoxRows>::kSmemBytes);
+}
+
+template <int kLayer, int kBoxRows>
+cudaError_t launch_one(const UmmaParams& p, cudaStream_t s) {
+  umma_kernel<kLayer, kBoxRows><<<g_num_sms, kThreads, Shape<kLayer, kBoxRows>::kSmemBytes, s>>>(p);
+  return cudaGetLastError();
+}
+
+int box_rows_of(int block_m) { return block_m <= 16 ? 16 : (block_m <= 32 ? 32 : (block_m <= 64 ? 64 : 128)); }
+
+template <int kLayer>
+cudaError_t launch_layer(const UmmaParams& p, int box, cudaStream_t s) {
+  switch (box) {
+    case 16: return launch_one<kLayer, 16>(p, s);
+    case 32: return launch_one<kLayer, 32>(p, s);
+    case 64: return launch_one<kLayer, 64>(p, s);
+    default: return launch_one<kLayer, 128>(p, s);
+  }
+}
+
+}  // namespace
+
+int prepare_umma(const MmoeGeometry& geo) {
+  (void)geo;
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return MMOE_ERR_CUDA;
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MMOE_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MMOE_ERR_CUDA;
+  cudaError_t e = cudaSuccess;
+  if (e == cudaSuccess) e = prepare_one<1, 16>();
+  if (e == cudaSuccess) e = prepare_one<1, 32>();
+  if (e == cudaSuccess) e = prepare_one<1, 64>();
+  if (e == cudaSuccess) e = prepare_one<1, 128>();
+  if (e == cudaSuccess) e = prepare_one<2, 16>();
+  if (e == cudaSuccess) e = prepare_one<2, 32>();
+  if (e == cudaSuccess) e = prepare_one<2, 64>();
+  if (e == cudaSuccess) e = prepare_one<2, 128>();
+  return e == cudaSuccess ? MMOE_OK : MMOE_ERR_CUDA;
+}
+
+cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m,
+                                cudaStream_t s) {
+  if (g_encode == nullptr || g_num_sms == 0) return cudaErrorNotReady;
+  const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
+  const int box = box_rows_of(block_m);
+  const bool has_shared = c.geo.num_shared_experts > 0 && w.shared_w13 != nullptr && m > 0;
+  const int64_t timeout_ns = (o.timeout_ms > 0 ? (int64_t)o.timeout_ms : 2000) * 1000000ll;
+
+  UmmaParams p1{};
+  int bad = 0;
+  bad |= make_weight_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
+  bad |= make_map(&p1.map_tok_routed, false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, box, false);
+  if (has_shared) {
+    bad |= make_weight_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
+    bad |= make_map(&p1.map_tok_shared, false, c.ws + c.lay.x, h, c.geo.num_max_tokens, box, false);
+  } else {
+    p1.map_w_shared = p1.map_w_routed;
+    p1.map_tok_shared = p1.map_tok_routed;
+  }
+  if (bad) return cudaErrorInvalidValue;
+  p1.plan = c.ws + c.lay.plan;
+  p1.wsf_routed = static_cast<const int32_t*>(w.w13_sf);
+  p1.wsf_shared = static_cast<const int32_t*>(w.shared_w13_sf);
+  p1.tsf_routed = c.at<int32_t>(c.lay.pool_sf);
+  p1.tsf_shared = c.at<int32_t>(c.lay.shared_x_sf);
+  p1.tsf_rows_routed = c.lay.pool_sf_rows;
+  p1.tsf_rows_shared = c.lay.shared_sf_rows;
+  p1.act_routed = c.at<uint8_t>(c.lay.act_x);
+  p1.act_shared = c.at<uint8_t>(c.lay.shared_act_x);
+  p1.act_sf_routed = c.at<uint8_t>(c.lay.act_sf);
+  p1.act_sf_shared = c.at<uint8_t>(c.lay.shared_act_sf);
+  p1.act_sf_rows_routed = c.lay.pool_sf_rows;
+  p1.act_sf_rows_shared = c.lay.shared_sf_rows;
+  p1.pool_w = c.at<float>(c.lay.pool_w);
+  p1.status = c.at<int32_t>(c.lay.status);
+  p1.timeout_ns = timeout_ns;
+  p1.e_local = el;
+  p1.num_ranks = c.geo.num_ranks;
+  p1.k_dim = h;
+  p1.rows_per_expert = 2 * inter;
+  p1.routed_sliced = w.w13_slice_stride > 0 ? 1 : 0;
+  p1.n_blocks = inter / kTileRows;
+  p1.hidden = h;
+  p1.inter = inter;
+  p1.clamp = o.activation_clamp;
+  p1.fast_math = o.fast_math;
+  p1.has_shared_weights = has_shared ? 1 : 0;
+
+  UmmaParams p2 = p1;
+  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
+  bad |= make_map(&p2.map_tok_routed, false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, box, false);
+  if (has_shared) {
+    bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0);
+    bad |= make_map(&p2.map_tok_shared, false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, box, false);
+  } else {
+    p2.map_w_shared = p2.map_w_routed;
+    p2.map_tok_shared = p2.map_tok_routed;
+  }
+  if (bad) return cudaErrorInvalidValue;
+  p2.wsf_routed = static_cast<const int32_t*>(w.w2_sf);
+  p2.wsf_shared = static_cast<const int32_t*>(w.shared_w2_sf);
+  p2.tsf_routed = c.at<int32_t>(c.lay.act_sf);
+  p2.tsf_shared = c.at<int32_t>(c.lay.shared_act_sf);
+  p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
+  p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
+  p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
+  p2.k_dim = inter;
+  p2.rows_per_expert = h;
+  p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
+  p2.n_blocks = h / kTileRows;
+
+  cudaError_t e = launch_layer<1>(p1, box, s);
+  if (e != cudaSuccess) return e;
+  return launch_layer<2>(p2, box, s);
+}
+
+}  // namespace mmoe
