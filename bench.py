@@ -1,0 +1,357 @@
+"""Benchmark of the MegaMoE expert layer (routed MXFP8 x MXFP4 experts + one fused FP8 shared expert).
+
+    python bench.py --gpus N --steps K --warmup W              # this backend (CUDA, sm_100a)
+    python bench.py --impl reference --gpus N --steps K --warmup W   # the reference arithmetic on the host cores
+
+One step = one pass of the hot path over one batch of synthetic input: input staging (BF16 -> MXFP8) + the layer call.
+Workload at N = 1: H=5120, I=2304, E=384 physical experts, top-6, one shared expert, all experts resident, M=3840
+tokens; at N > 1 the experts are sharded E/N per rank (expert parallelism) and every rank brings M=3840 tokens of its
+own (weak scaling).  Inputs are seeded synthetic tensors with the shapes and distributions of the reference's harness.
+Every step streams gigabytes of distinct weights, far more than the 126 MB L2, so no cache flush is needed between
+steps; the decode points of the sweep rotate through several routings for the same reason.
+
+Prints ONE JSON line (rank 0).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, I, E, K = 5120, 2304, 384, 6
+M_HEADLINE = 3840
+SWEEP = (1, 8, 64, 256, 1024, 2048, 3840)
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 8 and r[2].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 8 for i in range(4) if r[4 + i].lower() == "active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle (a restatement of the reference's arithmetic; the reference ships no CPU
+# forward of the layer) on the host cores, on a bounded sample of the workload
+# ---------------------------------------------------------------------------------------------------------------------
+def cpu_reference(steps: int, warmup: int):
+    from oracle import mmoe_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    e_sample, m_sample = 32, 128
+    experts = O.make_experts(e_sample, H, I, seed=0)
+    shared = O.make_shared_expert(H, I, seed=1000)
+    deq = [ew.dequant() for ew in experts]          # dequantisation happens once, outside the timed region
+    sdeq = shared.dequant()
+    hid = O.make_hidden(m_sample, H, 0)
+    ids, w = O.make_routing(m_sample, e_sample, K, 0)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.moe_layer([hid], [ids], [w], experts, shared, 10.0, dequantized=deq, shared_dequantized=sdeq)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    sample = (f"M={m_sample} tokens, top-{K}, {e_sample} of the {E} experts resident (FP32-dequantised weights of all "
+              f"{E} would need 54 GB), one shared expert; quantise+dispatch+GEMM1+SwiGLU/requant+GEMM2+combine, "
+              f"weight dequantisation excluded; median of {len(times)} passes")
+    return m_sample / t, t, cores, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 8))
+    value, t, cores, sample = cpu_reference(steps, min(args.warmup, 2))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 2), "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (dequantised MXFP8 x MXFP4)", "data": "synthetic",
+        "config": {"workload": f"MegaMoE layer H={H} I={I} E={E} top-{K} 1 shared expert, EP{args.gpus}, M={M_HEADLINE}/rank",
+                   "impl_note": "CPU restatement of the reference arithmetic (the reference ships no CPU forward and its "
+                                "GPU kernel runs on compute capability 10.7 only)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# this backend
+# ---------------------------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import ctypes
+
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend import _native
+    from vllm_plugin_b200.backend.workspace import SingleRankGroup
+    from vllm_plugin_b200.testing import SyntheticLayer, layer_work, make_hidden, make_routing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    group = SingleRankGroup()
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    e_local = E // world
+    t_cap = 3840
+
+    syn = SyntheticLayer(H, I, e_local, True, dev, seed=0, first_expert=rank * e_local)
+    buf = api.get_symm_buffer_for_mega_moe(group, E, t_cap, K, H, I, 1)
+    api.precompile_mega_moe_variants(world, E, t_cap, K, H, I, 1, activation_clamp=10.0)
+    lib = _native.load()
+    stats = torch.zeros(e_local, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def inputs(m, seed):
+        hid = make_hidden(m, H, seed + 17 * rank, dev)
+        ids, w = make_routing(m, E, K, seed + 31 * rank, dev)
+        return hid, ids, w
+
+    def layer_call(hid, ids, w, y):
+        api.stage_inputs_for_mega_moe(buf, hid, ids, w)
+        api.fp8_fp4_mega_moe(y, syn.l1, syn.l2, buf, syn.shared_l1, syn.shared_l2,
+                             cumulative_local_expert_recv_stats=stats, activation_clamp=10.0, fast_math=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- headline: K timed steps at M = 3840 per rank, inputs resident in HBM ----------------------------------
+    m = M_HEADLINE
+    hid, ids, w = inputs(m, 1)
+    y = torch.empty((m, H), dtype=torch.bfloat16, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        layer_call(hid, ids, w, y)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        layer_call(hid, ids, w, y)
+    ev1.record(stream)
+    barrier()
+    step_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
+    value = world * m / (step_ms * 1e-3)
+    launches_per_step = 9          # quantiser, 3 route-ordering passes, plan, place, GEMM1, GEMM2, combine
+
+    # ---- end to end through the public API with host buffers (pinned): H2D of the step's inputs, D2H of y -------
+    hid_h, ids_h, w_h = hid.cpu().pin_memory(), ids.cpu().pin_memory(), w.cpu().pin_memory()
+    y_h = torch.empty((m, H), dtype=torch.bfloat16).pin_memory()
+    hid_d, ids_d, w_d = torch.empty_like(hid), torch.empty_like(ids), torch.empty_like(w)
+
+    def e2e_step():
+        hid_d.copy_(hid_h, non_blocking=True)
+        ids_d.copy_(ids_h, non_blocking=True)
+        w_d.copy_(w_h, non_blocking=True)
+        layer_call(hid_d, ids_d, w_d, y)
+        y_h.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    ev1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = hid_h.numel() * 2 + ids_h.numel() * 8 + w_h.numel() * 4
+    d2h = y_h.numel() * 2
+
+    # ---- per-kernel timing of the dominant kernel (grouped GEMM1), live, with events on the launch stream --------
+    line_extra = {}
+    roofline = None
+    if world == 1:
+        peak, peak_kind = measured_peaks()
+        geo = ctypes.byref(buf.geo)
+        wst = _weights_struct(syn)
+        bm = api.get_block_m_for_mega_moe(1, E, t_cap, m, K)
+        opts1 = _native.MmoeOptions(10.0, 1, 0, 2000, 1)
+        opts2 = _native.MmoeOptions(10.0, 1, 0, 2000, 2)
+        sp = stream.cuda_stream
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t1, t2 = [], []
+        for it in range(3 + args.steps):
+            api.stage_inputs_for_mega_moe(buf, hid, ids, w)
+            _native.check(lib.mmoe_dispatch_count(geo, buf.base_ptr, m, sp))
+            _native.check(lib.mmoe_dispatch_place(geo, buf.base_ptr, m, bm, None, sp))
+            evs[0].record(stream)
+            _native.check(lib.mmoe_experts(geo, buf.base_ptr, ctypes.byref(wst), ctypes.byref(opts1), m, bm, sp))
+            evs[1].record(stream)
+            _native.check(lib.mmoe_experts(geo, buf.base_ptr, ctypes.byref(wst), ctypes.byref(opts2), m, bm, sp))
+            evs[2].record(stream)
+            _native.check(lib.mmoe_combine(geo, buf.base_ptr, y.data_ptr(), m, sp))
+            torch.cuda.synchronize(dev)
+            if it >= 3:
+                t1.append(evs[0].elapsed_time(evs[1]))
+                t2.append(evs[1].elapsed_time(evs[2]))
+        distinct = int(torch.unique(ids[ids >= 0]).numel())
+        routes = int((ids >= 0).sum())
+        w13_bytes = distinct * (I * H + 2 * I * H // 32) + (2 * I * H + 2 * I * H // 32)     # routed + shared W13 and scales
+        w2_bytes = distinct * (H * I // 2 + H * I // 32) + (H * I + H * I // 32)
+        g1_ms, g2_ms = statistics.mean(t1), statistics.mean(t2)
+        ach = w13_bytes / (g1_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "umma_kernel<1> (grouped GEMM1 + SwiGLU/requant)", "achieved": ach,
+                    "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": f"of {peak_kind}",
+                    "traffic": None, "algorithmic_bytes_per_launch": w13_bytes, "ms_per_launch": g1_ms}
+        flops, nbytes = layer_work(routes, m, distinct, H, I, True)
+        line_extra["kernels"] = {
+            "gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "gemm2_gbs": w2_bytes / (g2_ms * 1e-3) / 1e9,
+            "layer_algorithmic_gbs": nbytes / (step_ms * 1e-3) / 1e9, "layer_tflops": flops / (step_ms * 1e-3) / 1e12,
+            "layer_hbm_frac": nbytes / (step_ms * 1e-3) / 1e9 / peak}
+
+        # ---- token sweep (latency per call; decode points rotate through 8 routings so weights come from HBM) ----
+        sweep = {}
+        for ms in SWEEP if not args.no_sweep else ():
+            sets = [inputs(ms, 100 + j) for j in range(8 if ms <= 256 else 2)]
+            ys = torch.empty((ms, H), dtype=torch.bfloat16, device=dev)
+            for j in range(3):
+                layer_call(*sets[j % len(sets)], ys)
+            reps = 24 if ms <= 256 else 8
+            es = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+            for j in range(reps):
+                es[j][0].record(stream)
+                layer_call(*sets[j % len(sets)], ys)
+                es[j][1].record(stream)
+            torch.cuda.synchronize(dev)
+            lat = sorted(a.elapsed_time(b) * 1e3 for a, b in es)
+            p50 = lat[len(lat) // 2]
+            uniq = statistics.mean(int(torch.unique(s[1]).numel()) for s in sets)
+            fl, nb = layer_work(ms * K, ms, int(round(uniq)), H, I, True)
+            sweep[str(ms)] = {"p50_us": p50, "p90_us": lat[int(len(lat) * 0.9)], "tokens_per_s": ms / (p50 * 1e-6),
+                              "gbs": nb / (p50 * 1e-6) / 1e9, "hbm_frac": nb / (p50 * 1e-6) / 1e9 / peak,
+                              "tflops": fl / (p50 * 1e-6) / 1e12, "experts_hit": uniq}
+        line_extra["sweep"] = sweep
+        if "64" in sweep:
+            line_extra["p50_us_at_M64"] = sweep["64"]["p50_us"]
+
+    from vllm_plugin_b200.backend.frontend import read_status
+    read_status(buf)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "mxfp8 x mxfp4 (e4m3 x e2m1, ue8m0 scales per 32), fp32 accumulate, bf16 out", "data": "synthetic",
+            "config": {"workload": f"MegaMoE layer H={H} I={I} E={E} top-{K} 1 shared expert, EP{world}, M={m}/rank",
+                       "parallelism": f"ep{world}", "l2": "inputs larger than L2 (each step streams the packed weights of every expert hit)"},
+            "e2e": {"value": world * m / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if roofline is not None:
+            line["roofline"] = roofline
+        line.update(line_extra)
+        if world == 1 and not args.no_cpu_baseline:
+            v, t, cores, sample = cpu_reference(3, 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _weights_struct(syn):
+    from vllm_plugin_b200.backend import _native
+    w = _native.MmoeWeights()
+    w.w13, w.w13_sf = syn.l1[0].data_ptr(), syn.l1[1].data_ptr()
+    w.w2, w.w2_sf = syn.l2[0].data_ptr(), syn.l2[1].data_ptr()
+    w.shared_w13, w.shared_w13_sf = syn.shared_l1[0].data_ptr(), syn.shared_l1[1].data_ptr()
+    w.shared_w2, w.shared_w2_sf = syn.shared_l2[0].data_ptr(), syn.shared_l2[1].data_ptr()
+    return w
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--experts", type=int, default=E, help="physical experts (smaller values give a small profiling case)")
+    ap.add_argument("--tokens", type=int, default=M_HEADLINE, help="tokens per rank of the timed step")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    globals()["E"] = args.experts
+    globals()["M_HEADLINE"] = args.tokens
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -124,6 +124,7 @@ typedef struct MmoeOptions {
   int32_t fast_math;        /* 1: ex2.approx / rcp.approx sigmoid, 0: IEEE expf and division */
   int32_t engine;           /* 0: tcgen05 tensor-core kernels; 1: scalar validation kernels (tests only) */
   int32_t timeout_ms;       /* bound of every device-side wait; <= 0 selects the default (2000) */
+  int32_t layer_mask;       /* 0 or 3: both grouped GEMMs; 1: GEMM1 (+SwiGLU) only; 2: GEMM2 only (per-kernel timing) */
 } MmoeOptions;
 
 /* The steps of one forward call.  At EP1 `mmoe_forward` runs all of them; at EP>1 the host interleaves the three

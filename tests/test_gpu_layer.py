@@ -1,0 +1,147 @@
+"""GPU parity of the whole layer against the CPU oracle on identical seeded inputs, through the package's public API
+(which calls the C ABI).  Tolerance of the BF16 output: relative L2 <= 1e-3 and max_abs <= 2e-2; one BF16 ulp of the
+reference is larger than 2e-2 wherever |y| >= 4, and a one-ulp disagreement is inherent to the FP32 summation order, so
+the element-wise bound is max(2e-2, one BF16 ulp of the reference value)."""
+
+import pytest
+import torch
+
+import helpers as H
+from helpers import O
+
+pytestmark = pytest.mark.gpu
+
+REL_L2 = 1e-3
+MAX_ABS = 2e-2
+
+
+def assert_parity(y, ref, what=""):
+    a, b = y.float().cpu(), ref.float()
+    assert torch.isfinite(a).all(), what
+    rel = float((a - b).norm() / b.norm().clamp(min=1e-30))
+    ulp = torch.pow(2.0, torch.floor(torch.log2(b.abs().clamp(min=2.0 ** -126))) - 7)
+    bound = torch.clamp(ulp, min=MAX_ABS)
+    worst = float(((a - b).abs() - bound).max())
+    assert rel <= REL_L2, f"{what}: rel_l2 {rel}"
+    assert worst <= 0, f"{what}: an element exceeds max(2e-2, 1 ulp) by {worst}"
+
+
+SMALL = dict(hidden=512, inter=256, num_experts=8, num_topk=2)
+
+
+@pytest.mark.parametrize("engine", [0, 1])
+@pytest.mark.parametrize("m", [1, 5, 33, 130])
+@pytest.mark.parametrize("shared", [True, False])
+def test_small_layer_matches_oracle(engine, m, shared):
+    layer = H.make_layer(shared=shared, seed=m, **SMALL)
+    hid = O.make_hidden(m, layer.hidden, 1)
+    ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 2, mask_frac=0.1 if m > 1 else 0.0)
+    y, _ = H.run_layer(layer, hid, ids, w, engine=engine)
+    assert_parity(y, H.oracle_layer(layer, hid, ids, w), f"engine {engine} m {m}")
+
+
+@pytest.mark.parametrize("bm", [16, 32, 64, 128, 192, 240])
+def test_every_block_m_variant(bm):
+    """Forced BLOCK_M with ~150 tokens per expert: several blocks per expert, partially filled last blocks, and for
+    BLOCK_M >= 128 chunks of more than 112 rows that are split into two tensor-core tiles."""
+    from vllm_plugin_b200 import api
+    layer = H.make_layer(shared=True, seed=3, **SMALL)
+    m = 600
+    hid = O.make_hidden(m, layer.hidden, 4)
+    ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 5, zipf_s=1.2)
+    api.set_kernel_options(block_m=bm)
+    try:
+        y, buf = H.run_layer(layer, hid, ids, w)
+        assert buf.plan_tables()[0]["block_m"] == bm
+    finally:
+        api.set_kernel_options(block_m=0)
+    assert_parity(y, H.oracle_layer(layer, hid, ids, w), f"block_m {bm}")
+
+
+def test_options_fast_math_clamp_and_localized_weights():
+    layer = H.make_layer(shared=True, seed=9, **SMALL)
+    hid = (O.make_hidden(40, layer.hidden, 1).float() * 6).to(torch.bfloat16)       # large activations: the clamp bites
+    ids, w = O.make_routing(40, layer.num_experts, layer.num_topk, 2)
+    for clamp in (10.0, 0.5, None):
+        ref = H.oracle_layer(layer, hid, ids, w, clamp=clamp)
+        for fast in (True, False):
+            y, _ = H.run_layer(layer, hid, ids, w, clamp=clamp, fast_math=fast)
+            assert_parity(y, ref, f"clamp {clamp} fast_math {fast}")
+    y0, _ = H.run_layer(layer, hid, ids, w)
+    y1, _ = H.run_layer(layer, hid, ids, w, localized=True)                         # two-slice routed weights
+    assert torch.equal(y0, y1)
+
+
+def test_masked_tokens_padding_and_empty_call():
+    layer = H.make_layer(shared=False, seed=11, **SMALL)
+    m = 20
+    hid = O.make_hidden(m, layer.hidden, 1)
+    ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 2)
+    pad = torch.zeros(m, dtype=torch.bool)
+    pad[[0, 7, 19]] = True
+    y, _ = H.run_layer(layer, hid, ids, w, pad=pad)
+    ref = H.oracle_layer(layer, hid, ids, w, pad=pad)
+    assert_parity(y, ref, "padding")
+    assert float(y[pad.cuda()].float().abs().max()) == 0.0          # no valid slot and no shared expert: exact zeros
+    y_empty, _ = H.run_layer(layer, hid[:0], ids[:0], w[:0])
+    assert y_empty.shape == (0, layer.hidden)
+
+
+def test_outputs_do_not_depend_on_batch_composition():
+    """Size-independent property: a token's output is bit-identical whatever other tokens share the call (columns of the
+    tensor-core tiles are independent and the K order is fixed)."""
+    layer = H.make_layer(shared=True, seed=13, **SMALL)
+    m = 300
+    hid = O.make_hidden(m, layer.hidden, 1)
+    ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 2)
+    y, _ = H.run_layer(layer, hid, ids, w)
+    perm = torch.randperm(m, generator=torch.Generator().manual_seed(0))
+    y_perm, _ = H.run_layer(layer, hid[perm], ids[perm], w[perm])
+    assert torch.equal(y_perm.cpu(), y.cpu()[perm])
+    y_head, _ = H.run_layer(layer, hid[:17], ids[:17], w[:17])
+    assert torch.equal(y_head.cpu(), y.cpu()[:17])
+
+
+def test_reference_cpu_configuration():
+    """The CPU-runnable configuration of the benchmark: H=5120, I=2304, E=32, top-6, one shared expert, M=128, seed 0."""
+    layer = H.make_layer(5120, 2304, 32, 6, True, seed=0)
+    hid = O.make_hidden(128, 5120, 0)
+    ids, w = O.make_routing(128, 32, 6, 0)
+    y, buf = H.run_layer(layer, hid, ids, w)
+    assert buf.plan_tables()[0]["block_m"] == 32
+    assert_parity(y, H.oracle_layer(layer, hid, ids, w), "config 0")
+
+
+def test_full_size_engines_agree_and_permutation_invariance():
+    """E=384 resident experts (7.2 GB of packed weights generated on the GPU), M=256 decode-side point: the tensor-core
+    kernels against the scalar validation kernels on the same pool, per-expert counts against the routing, and the
+    batch-composition property at full size."""
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend.workspace import SingleRankGroup
+    from vllm_plugin_b200.testing import SyntheticLayer, make_hidden, make_routing
+    e, k, h, i, m = 384, 6, 5120, 2304, 256
+    syn = SyntheticLayer(h, i, e, True, "cuda", seed=1)
+    buf = api.get_symm_buffer_for_mega_moe(SingleRankGroup(), e, 3840, k, h, i, 1)
+    hid = make_hidden(m, h, 1, "cuda")
+    ids, w = make_routing(m, e, k, 2, "cuda")
+    stats = torch.zeros(e, dtype=torch.int32, device="cuda")
+
+    def run(hh, ii, ww, engine, st=None):
+        y = torch.empty((hh.shape[0], h), dtype=torch.bfloat16, device="cuda")
+        api.set_kernel_options(engine=engine)
+        try:
+            api.stage_inputs_for_mega_moe(buf, hh, ii, ww)
+            api.fp8_fp4_mega_moe(y, syn.l1, syn.l2, buf, syn.shared_l1, syn.shared_l2,
+                                 cumulative_local_expert_recv_stats=st, activation_clamp=10.0)
+        finally:
+            api.set_kernel_options(engine=0)
+        from vllm_plugin_b200.backend.frontend import read_status
+        read_status(buf)
+        return y
+
+    y_tc = run(hid, ids, w, 0, stats)
+    y_sc = run(hid, ids, w, 1)
+    assert torch.equal(stats.cpu().long(), torch.bincount(ids.cpu().flatten(), minlength=e))
+    assert_parity(y_tc, y_sc.cpu(), "tensor-core vs scalar engine, E=384")
+    perm = torch.randperm(m, generator=torch.Generator().manual_seed(1)).cuda()
+    assert torch.equal(run(hid[perm], ids[perm], w[perm], 0), y_tc[perm])

@@ -1,0 +1,135 @@
+"""Host logic of the package (BLOCK_M, variants, admission gate, weight layouts, C-ABI export) against the reference's
+golden outputs.  No GPU: nothing here launches a kernel."""
+
+import ctypes
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import ROOT
+
+GOLD = os.path.join(ROOT, "tests", "golden")
+
+
+@pytest.fixture(scope="module")
+def host_logic():
+    with open(os.path.join(GOLD, "host_logic.json")) as f:
+        return json.load(f)
+
+
+def test_block_m_python_and_c(host_logic):
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend import _native
+    lib = _native.load()
+    ms = host_logic["ms"]
+    for key, expect in host_logic["block_m"].items():
+        r, e, k = map(int, key.split(","))
+        assert [api.get_block_m_for_mega_moe(r, e, 0, m, k) for m in ms] == expect, key
+        assert [lib.mmoe_block_m(r, e, m, k) for m in ms] == expect, key
+
+
+def test_block_m_variants(host_logic):
+    from vllm_plugin_b200.backend import heuristics as H
+    for key, expect in host_logic["variants"].items():
+        r, e, k, t = map(int, key.split(","))
+        assert list(H.get_block_m_variants(r, e, k, t)) == expect, key
+
+
+def test_token_alignment_and_tables(host_logic):
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend import heuristics as H
+    assert api.get_token_alignment_for_mega_moe() == host_logic["token_alignment"] == 1920
+    assert {",".join(map(str, k)): list(v[0]) for k, v in H.VALIDATED_GEOMETRIES.items()} == host_logic["validated_geometries"]
+    assert {",".join(map(str, k)): [list(p) for p in v[0]] for k, v in H.VALIDATED_EP_GEOMETRIES.items()} == host_logic["validated_ep_geometries"]
+    assert H.MIN_VALIDATED_EXPERTS_PER_RANK == host_logic["min_experts_per_rank"]
+
+
+def test_admission_gate_matches_reference(host_logic):
+    from vllm_plugin_b200 import api
+    for case in host_logic["admission"]:
+        reason = api.get_unsupported_reason_for_mega_moe(*case["args"], **case["kwargs"])
+        assert (reason is None) == case["admitted"], (case, reason)
+        if case["unvalidated"]:
+            assert "has not been validated" in reason
+
+
+def test_admission_gate_is_total():
+    from vllm_plugin_b200 import api
+    for bad in [(None, 384, 2560, 6, 5120, 2304), ("x", 1, 1, 1, 1, 1), (1, 384, 2560, 6, 5120.5, 2304), (1, [], 1, 1, 1, 1)]:
+        reason = api.get_unsupported_reason_for_mega_moe(*bad)
+        assert isinstance(reason, str) and reason
+
+
+def test_weight_transform_against_reference_layouts():
+    from vllm_plugin_b200.backend import weights as W
+    g = np.load(os.path.join(GOLD, "weights.npz"))
+    sf13 = torch.from_numpy(g["sf13"])
+    e_l, n13, k32 = sf13.shape
+    l13 = W.sf_to_required_layout(sf13, n13, k32 * 32, e_l)
+    assert list(l13.stride()) == list(g["l13_strides"])
+    assert np.array_equal(l13.contiguous().numpy(), g["l13"])
+    w13 = torch.from_numpy(g["w13"])
+    w2 = torch.from_numpy(g["w2"])
+    sf2 = torch.from_numpy(g["sf2"])
+    l2 = W.sf_to_required_layout(sf2, sf2.shape[1], sf2.shape[2] * 32, e_l)
+    (t13, t13sf), (t2, t2sf) = W.transform_weights_for_mega_moe((w13, l13), (w2, l2))
+    assert t13 is w13 and t2 is w2                                     # packed weights are used as loaded
+    assert np.array_equal(t13sf.contiguous().numpy(), g["utccp13"])   # 4x32 transpose, no gate/up interleave
+    assert np.array_equal(t2sf.contiguous().numpy(), g["t2sf"])       # identical to the reference for L2
+    assert t13sf.stride() == l13.stride()
+    with pytest.raises(AssertionError):
+        W.transform_weights_for_mega_moe((w13, l13), (w2, l2), activation="silu")
+
+
+def test_localize_shape_and_round_trip():
+    from vllm_plugin_b200.backend import locality as L
+    t = torch.arange(3 * 8 * 6, dtype=torch.int8).view(3, 8, 6)
+    loc = L.localize(t)
+    assert tuple(loc.shape) == (2, 3, 4, 6)
+    assert (loc.stride(0) * loc.element_size()) % (2 << 20) == 0
+    assert L.is_canonical_localized(loc)
+    assert torch.equal(loc.movedim(0, 1).flatten(1, 2), t)             # how the reference's tests undo the split
+    assert torch.equal(L.delocalize(loc), t)
+
+
+def test_library_exports_every_declared_symbol():
+    from vllm_plugin_b200.backend import _native
+    header = open(os.path.join(ROOT, "include", "mmoe.h")).read()
+    declared = set(re.findall(r"\b(mmoe_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_native.EXPORTED_SYMBOLS)
+    lib = ctypes.CDLL(_native.library_path())
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _native.load().mmoe_abi_version() == 1
+
+
+def test_layout_is_consistent():
+    from vllm_plugin_b200.backend import _native
+    geo = _native.MmoeGeometry(8, 3, 392, 6, 5120, 2304, 1, 3840)
+    lay = _native.layout_of(geo)
+    offs = [(n, getattr(lay, n)) for n in _native._LAYOUT_FIELDS[1:32] if n not in ("shared_sf_rows",)]
+    vals = [v for _, v in offs]
+    assert vals == sorted(vals) and all(v % 1024 == 0 for v in vals)
+    assert lay.total_bytes > vals[-1]
+    assert lay.shared_sf_rows == -(-3840 // 8) * 128
+    assert lay.max_routes == 3840 * 6
+    with pytest.raises(AssertionError):
+        _native.layout_of(_native.MmoeGeometry(8, 3, 390, 6, 5120, 2304, 1, 3840))
+    with pytest.raises(AssertionError):
+        _native.layout_of(_native.MmoeGeometry(1, 0, 384, 6, 5120, 2304, 1, 2560))   # capacity must be aligned to 1920
+    with pytest.raises(NotImplementedError):
+        _native.layout_of(_native.MmoeGeometry(1, 0, 384, 6, 5120, 2304, 2, 3840))
+
+
+def test_import_is_light():
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r); import vllm_plugin_b200, vllm_plugin_b200.api as a; "
+            "vllm_plugin_b200.register(); a.get_unsupported_reason_for_mega_moe(1, 384, 2560, 6, 5120, 2304, 1); a.get_token_alignment_for_mega_moe(); "
+            "bad = [m for m in ('torch', 'vllm', 'triton') if m in sys.modules]; assert not bad, bad" % ROOT)
+    env = {k: v for k, v in os.environ.items() if k != "VLLM_PLUGINS"}
+    subprocess.run([sys.executable, "-c", code], check=True, env=env)

@@ -57,7 +57,7 @@ class MmoeWeights(ctypes.Structure):
 
 class MmoeOptions(ctypes.Structure):
     _fields_ = [("activation_clamp", ctypes.c_float), ("fast_math", ctypes.c_int32), ("engine", ctypes.c_int32),
-                ("timeout_ms", ctypes.c_int32)]
+                ("timeout_ms", ctypes.c_int32), ("layer_mask", ctypes.c_int32)]
 
 
 _lib: Optional[ctypes.CDLL] = None

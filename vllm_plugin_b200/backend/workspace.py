@@ -49,7 +49,9 @@ class SymmBuffer:
         assert self.buffer.data_ptr() % 1024 == 0
         self.buffer.zero_()
         if group.size() > 1:
-            group.barrier()
+            work = group.barrier()
+            if hasattr(work, "wait"):
+                work.wait()
         torch.cuda.synchronize(device)
         self._build_views()
 

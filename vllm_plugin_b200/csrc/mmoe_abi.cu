@@ -297,6 +297,7 @@ int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
     if ((reinterpret_cast<uintptr_t>(p) & 31u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "weight tensors must be 32-byte aligned");
   if (!(opt->activation_clamp > 0.f)) return fail(MMOE_ERR_INVALID_ARGUMENT, "activation_clamp must be positive (use +inf for none)");
   MmoeOptions o = *opt;
+  if (o.layer_mask < 0 || o.layer_mask > 3) return fail(MMOE_ERR_INVALID_ARGUMENT, "layer_mask=%d outside [0, 3]", o.layer_mask);
   o.activation_clamp = bf16_round_host(o.activation_clamp);   // the clamp is applied to BF16 values
   cudaError_t e;
   if (o.engine == 1) {

@@ -580,9 +580,12 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
   p2.n_blocks = h / kTileRows;
 
-  cudaError_t e = launch_layer<1>(p1, box, s);
+  const int mask = o.layer_mask == 0 ? 3 : o.layer_mask;
+  cudaError_t e = cudaSuccess;
+  if (mask & 1) e = launch_layer<1>(p1, box, s);
   if (e != cudaSuccess) return e;
-  return launch_layer<2>(p2, box, s);
+  if (mask & 2) e = launch_layer<2>(p2, box, s);
+  return e;
 }
 
 }  // namespace mmoe
