@@ -19,7 +19,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -46,42 +45,52 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event (throttle) reasons of one GPU every few milliseconds through NVML while a
+    timed region runs (read-only queries)."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []
-        self.proc = None
+        self.sm, self.mask = [], 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001 - no NVML: the clocks entry reports no samples
+            self._nvml = None
+
+    def _loop(self):
+        n = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM)))
+                self.mask |= int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+            except Exception:  # noqa: BLE001
+                break
+            time.sleep(0.002)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+        if self._nvml is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
 
     def stop(self):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
-        sm = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) >= 8 and r[2].replace(".", "").isdigit()]
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = sorted({names[i] for r in self.rows if len(r) >= 8 for i in range(4) if r[4 + i].lower() == "active"})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        reasons = [name for name, bit in self.REASONS if self.mask & bit]
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.sm)}
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -155,6 +164,7 @@ def run_ours(args):
         group = dist.group.WORLD
     e_local = E // world
     t_cap = 3840
+    sampler = ClockSampler(local_rank)      # NVML is initialised before anything is timed
 
     syn = SyntheticLayer(H, I, e_local, True, dev, seed=0, first_expert=rank * e_local)
     buf = api.get_symm_buffer_for_mega_moe(group, E, t_cap, K, H, I, 1)
@@ -191,7 +201,6 @@ def run_ours(args):
     y = torch.empty((m, H), dtype=torch.bfloat16, device=dev)
     for _ in range(max(args.warmup, 3)):
         layer_call(hid, ids, w, y)
-    sampler = ClockSampler(local_rank)
     barrier()
     if rank == 0:
         sampler.start()
@@ -275,15 +284,29 @@ def run_ours(args):
         # ---- token sweep (latency per call; decode points rotate through 8 routings so weights come from HBM) ----
         sweep = {}
         for ms in SWEEP if not args.no_sweep else ():
+            # each point is captured once as a CUDA graph per input set and replayed (the reference publishes CUDA-graph
+            # latencies); the sets rotate so that consecutive replays hit different experts and weights come from HBM
             sets = [inputs(ms, 100 + j) for j in range(8 if ms <= 256 else 2)]
             ys = torch.empty((ms, H), dtype=torch.bfloat16, device=dev)
+            graphs = []
+            side = torch.cuda.Stream(dev)
+            for hs, is_, ws in sets:
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    for _ in range(2):
+                        layer_call(hs, is_, ws, ys)
+                torch.cuda.current_stream(dev).wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    layer_call(hs, is_, ws, ys)
+                graphs.append(g)
             for j in range(3):
-                layer_call(*sets[j % len(sets)], ys)
+                graphs[j % len(graphs)].replay()
             reps = 24 if ms <= 256 else 8
             es = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
             for j in range(reps):
                 es[j][0].record(stream)
-                layer_call(*sets[j % len(sets)], ys)
+                graphs[j % len(graphs)].replay()
                 es[j][1].record(stream)
             torch.cuda.synchronize(dev)
             lat = sorted(a.elapsed_time(b) * 1e3 for a, b in es)
@@ -292,7 +315,8 @@ def run_ours(args):
             fl, nb = layer_work(ms * K, ms, int(round(uniq)), H, I, True)
             sweep[str(ms)] = {"p50_us": p50, "p90_us": lat[int(len(lat) * 0.9)], "tokens_per_s": ms / (p50 * 1e-6),
                               "gbs": nb / (p50 * 1e-6) / 1e9, "hbm_frac": nb / (p50 * 1e-6) / 1e9 / peak,
-                              "tflops": fl / (p50 * 1e-6) / 1e12, "experts_hit": uniq}
+                              "tflops": fl / (p50 * 1e-6) / 1e12, "experts_hit": uniq, "cuda_graph": True}
+            del graphs
         line_extra["sweep"] = sweep
         if "64" in sweep:
             line_extra["p50_us_at_M64"] = sweep["64"]["p50_us"]

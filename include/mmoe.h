@@ -102,13 +102,15 @@ int mmoe_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidd
                       int32_t ids_are_int64, const float* topk_weights, const uint8_t* is_padding, int32_t num_tokens,
                       int32_t shared_block_m, void* stream);
 
-/* Weights of one rank in the layout `transform_weights_for_mega_moe` of this backend produces. */
+/* Weights of one rank in the layout `transform_weights_for_mega_moe` produces, which is bit-identical to the
+ * reference's (backend/weights.py:120-145): W13 rows interleaved gate/up by 8 ([g0..7, u0..7, g8..15, ...]), scale words
+ * in the same row order and 4x32-transposed inside every 128-row block. */
 typedef struct MmoeWeights {
-  const void* w13;        /* packed E2M1 [E/R, 2I, H/2], rows [gate | up] */
-  const void* w13_sf;     /* int32 [E/R, H/128, 2I] (scale word w of row r at w*2I + r'), 4x32 transposed per 128 rows */
+  const void* w13;        /* packed E2M1 [E/R, 2I, H/2], stored rows gate/up interleaved by 8 */
+  const void* w13_sf;     /* int32 [E/R, H/128, 2I] (scale word w of stored row r at w*2I + r'), 4x32 transposed per 128 rows */
   const void* w2;         /* packed E2M1 [E/R, H, I/2] */
   const void* w2_sf;      /* int32 [E/R, I/128, H], 4x32 transposed per 128 rows */
-  const void* shared_w13; /* E4M3 [2I, H] or NULL */
+  const void* shared_w13; /* E4M3 [2I, H] (same gate/up interleave) or NULL */
   const void* shared_w13_sf;
   const void* shared_w2;  /* E4M3 [H, I] or NULL */
   const void* shared_w2_sf;
@@ -152,6 +154,11 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
 /* Copy the device status words to the host (synchronises the stream) and translate them: MMOE_OK or
  * MMOE_ERR_DEVICE_TIMEOUT.  Replaces the reference's device `trap` after a 300 s spin (backend/kernel/comm.py:229-250). */
 int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream);
+
+/* Process-wide tuning of the tensor-core kernels (the reference keeps such knobs in `KernelOptions`,
+ * backend/frontend.py:72-116): `prefetch_ahead` = K stages of weight traffic requested into L2 ahead of the
+ * shared-memory pipeline (< 0: built-in default, 0: off); `max_stages` = cap on the pipeline depth (0: no cap). */
+int mmoe_set_tuning(int32_t prefetch_ahead, int32_t max_stages);
 
 const char* mmoe_status_string(int code);
 const char* mmoe_last_error(void);   /* detail of the last failure on this thread */

@@ -77,9 +77,10 @@ def test_weight_transform_against_reference_layouts():
     sf2 = torch.from_numpy(g["sf2"])
     l2 = W.sf_to_required_layout(sf2, sf2.shape[1], sf2.shape[2] * 32, e_l)
     (t13, t13sf), (t2, t2sf) = W.transform_weights_for_mega_moe((w13, l13), (w2, l2))
-    assert t13 is w13 and t2 is w2                                     # packed weights are used as loaded
-    assert np.array_equal(t13sf.contiguous().numpy(), g["utccp13"])   # 4x32 transpose, no gate/up interleave
-    assert np.array_equal(t2sf.contiguous().numpy(), g["t2sf"])       # identical to the reference for L2
+    # bit-identical to the reference's transform: gate/up 8-row interleave + 4x32 scale transpose
+    assert np.array_equal(t13.numpy(), g["t13"]) and np.array_equal(t2.numpy(), g["t2"])
+    assert np.array_equal(t13sf.contiguous().numpy(), g["t13sf"]) and list(t13sf.stride()) == list(g["t13sf_strides"])
+    assert np.array_equal(t2sf.contiguous().numpy(), g["t2sf"])
     assert t13sf.stride() == l13.stride()
     with pytest.raises(AssertionError):
         W.transform_weights_for_mega_moe((w13, l13), (w2, l2), activation="silu")

@@ -6,11 +6,13 @@ int32 ``(E_l, N, ceil(K/128))`` with four UE8M0 bytes per word (byte ``b`` of wo
 MN-major (``stride(-2) == 1``), which is what :func:`sf_to_required_layout` produces from per-32 scales
 (``backend/weights.py:37-80``).
 
-Output = what the sm_100a kernels read.  The packed weights are left exactly as given: gate and up rows of a channel
-tile go to two separate tensor-memory accumulators, so no row interleave is needed (the reference interleaves eight
-rows, ``backend/weights.py:83-97``).  The scale words get the 4x32 transpose inside every 128-row block (stored position
-``4c + a`` holds row ``32a + c``, same as ``backend/weights.py:100-117``) so that each (128 rows, 128 K) block of scales
-is one contiguous 512-byte chunk in the order ``tcgen05.cp`` copies into tensor memory.
+Output = bit-identical to the reference's transform (``backend/weights.py:83-145``), which is also the layout the
+serving engine's native layer keeps its parameters in, so parameters loaded by that layer can be handed to the kernels
+unchanged: L1 weights and scales get the gate/up 8-row interleave (``[g0..7, u0..7, g8..15, u8..15, ...]``), then L1 and
+L2 scales get the 4x32 transpose inside every 128-row block (stored position ``4c + a`` holds row ``32a + c``), which
+makes each (128 rows, 128 K) block of scales one contiguous 512-byte chunk in the order ``tcgen05.cp`` copies into
+tensor memory.  The sm_100a kernels undo the interleave for free: a 5-D TMA box lands the 128 gate rows and the 128 up
+rows of a channel tile in two separate shared-memory tiles.
 """
 
 from __future__ import annotations
@@ -67,11 +69,26 @@ def transpose_sf_for_utccp(sf: torch.Tensor) -> torch.Tensor:
     return out.squeeze(0) if squeeze else out
 
 
+def interleave_weights(t: torch.Tensor, gran: int = 8) -> torch.Tensor:
+    """``[gate | up]`` rows -> ``[gate 0..7, up 0..7, gate 8..15, up 8..15, ...]`` along dim 1 (dim 0 for 2-D inputs)."""
+    assert t.dim() in (2, 3)
+    squeeze = t.dim() == 2
+    if squeeze:
+        t = t.unsqueeze(0)
+    g, n, *rest = t.shape
+    half = n // 2
+    assert half % gran == 0
+    gate = t[:, :half].reshape(g, half // gran, gran, *rest)
+    up = t[:, half:].reshape(g, half // gran, gran, *rest)
+    out = torch.empty_like(t).copy_(torch.stack([gate, up], dim=2).reshape(g, n, *rest))
+    return out.squeeze(0) if squeeze else out
+
+
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
                                    l2_weights: Tuple[torch.Tensor, torch.Tensor], activation: str = "swiglu"
                                    ) -> Tuple[Tuple[torch.Tensor, torch.Tensor], Tuple[torch.Tensor, torch.Tensor]]:
     """``(weights, sf)`` pairs in, ``(weights, sf)`` pairs out; shared-expert pairs (2-D tensors) go through the same
-    function.  The weight tensors are returned unchanged (same storage), only the scale words are rearranged."""
+    function."""
     assert activation in _SUPPORTED_ACTIVATIONS, f"Activation must be one of {_SUPPORTED_ACTIVATIONS}, got `{activation}`"
     if not isinstance(l1_weights, tuple) or not isinstance(l2_weights, tuple):
         raise NotImplementedError("only (weights, scale factors) pairs are supported (MXFP4 / MXFP8 weights)")
@@ -79,4 +96,6 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
         assert sf.dtype == torch.int32, "scale factors must be packed int32 words"
         assert sf.stride(-2) == 1, "scale factors must be MN-major (stride(-2) == 1)"
         assert w.shape[-2] == sf.shape[-2], "weights and scale factors disagree on the row count"
-    return (l1_weights[0], transpose_sf_for_utccp(l1_weights[1])), (l2_weights[0], transpose_sf_for_utccp(l2_weights[1]))
+    l1 = (interleave_weights(l1_weights[0]), transpose_sf_for_utccp(interleave_weights(l1_weights[1])))
+    l2 = (l2_weights[0], transpose_sf_for_utccp(l2_weights[1]))
+    return l1, l2

@@ -89,6 +89,12 @@ extern "C" {
 
 int mmoe_abi_version(void) { return 1; }
 
+int mmoe_set_tuning(int32_t prefetch_ahead, int32_t max_stages) {
+  if (max_stages < 0 || ((max_stages & 0xFFFF) > 0 && (max_stages & 0xFFFF) < 2)) return fail(MMOE_ERR_INVALID_ARGUMENT, "max_stages=%d must be 0 or >= 2", max_stages);
+  mmoe::set_tuning(prefetch_ahead, max_stages);
+  return MMOE_OK;
+}
+
 const char* mmoe_last_error(void) { return g_last_error.c_str(); }
 
 const char* mmoe_status_string(int code) {
@@ -295,6 +301,9 @@ int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
                            weights->shared_w13_sf, weights->shared_w2, weights->shared_w2_sf};
   for (const void* p : aligned)
     if ((reinterpret_cast<uintptr_t>(p) & 31u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "weight tensors must be 32-byte aligned");
+  if (weights->w13_slice_stride < 0 || weights->w2_slice_stride < 0 ||
+      (weights->w13_slice_stride > 0 && geo->intermediate % 256 != 0))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "two-slice W13 needs intermediate %% 256 == 0 and non-negative slice strides");
   if (!(opt->activation_clamp > 0.f)) return fail(MMOE_ERR_INVALID_ARGUMENT, "activation_clamp must be positive (use +inf for none)");
   MmoeOptions o = *opt;
   if (o.layer_mask < 0 || o.layer_mask > 3) return fail(MMOE_ERR_INVALID_ARGUMENT, "layer_mask=%d outside [0, 3]", o.layer_mask);

@@ -171,5 +171,6 @@ cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s);
 cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 int prepare_umma(const MmoeGeometry& geo);   // returns an MMOE_* code
+void set_tuning(int prefetch_ahead, int max_stages);
 
 }  // namespace mmoe

@@ -499,16 +499,18 @@ __global__ void __launch_bounds__(128) simt_l1_kernel(
     const bool shared = tile.expert == kSharedExpert;
     const int e = shared ? 0 : tile.expert;
     const int64_t wrow_bytes = fp8_weights ? h : h / 2;
-    const uint8_t* wg = weight_row_ptr(w13, e, c, 2 * inter, wrow_bytes, slice_stride);
-    const uint8_t* wu = weight_row_ptr(w13, e, inter + c, 2 * inter, wrow_bytes, slice_stride);
+    // stored W13 rows: [g0..7, u0..7, g8..15, u8..15, ...]
+    const int row_g = 16 * (c / 8) + (c % 8), row_u = row_g + 8;
+    const uint8_t* wg = weight_row_ptr(w13, e, row_g, 2 * inter, wrow_bytes, slice_stride);
+    const uint8_t* wu = weight_row_ptr(w13, e, row_u, 2 * inter, wrow_bytes, slice_stride);
     const int32_t* wsf = w13_sf + (int64_t)e * (h / 128) * 2 * inter;
     for (int i = 0; i < tile.n_valid; ++i) {
       const uint8_t* xr = tok_x + (int64_t)(tile.row0 + i) * h;
       float accg = 0.f, accu = 0.f;
       for (int g = 0; g < h / 32; ++g) {
         const float sx = ue8m0_to_float(token_sf_byte(tok_sf, tok_sf_rows, tile, i, g));
-        const float sg = ue8m0_to_float(weight_sf_byte(wsf, 2 * inter, c, g));
-        const float su = ue8m0_to_float(weight_sf_byte(wsf, 2 * inter, inter + c, g));
+        const float sg = ue8m0_to_float(weight_sf_byte(wsf, 2 * inter, row_g, g));
+        const float su = ue8m0_to_float(weight_sf_byte(wsf, 2 * inter, row_u, g));
         float dg, du;
         if (fp8_weights) {
           dg = dot_group<true>(xr + g * 32, wg + g * 32);

@@ -11,8 +11,9 @@
 //
 //   warp 0     producer: one thread issues the TMA tile loads (packed FP4 expands to byte containers on the way into
 //              shared memory; no cluster multicast) and 512-byte bulk copies of the scale chunks, per 128-K stage
-//   warp 1     MMA: one thread copies the scales into TMEM (tcgen05.cp) and issues 4 (x2 for layer 1) UMMAs per stage,
-//              committing each stage's shared memory back to the producer and each finished accumulator to the epilogue
+//   warps 1,6  MMA: one warp per weight tile of the stage; an elected lane copies the scales into TMEM (tcgen05.cp) and
+//              issues 4 UMMAs per stage, committing the stage's shared memory back to the producer and the finished
+//              accumulator to the epilogue
 //   warps 2-5  epilogue: TMEM -> registers (thread = weight row, columns = tokens), fused math, global stores
 //
 // Persistent CTAs (one per SM) walk a static task list (tile, 128-row weight block); TMEM accumulators are double
@@ -20,6 +21,7 @@
 // expires the CTA records {kernel, role, block} in the status words, lets its in-flight copies land, frees its TMEM and
 // returns; nothing traps.
 #include <cuda.h>
+#include <stdio.h>
 
 #include "mmoe_common.cuh"
 
@@ -27,9 +29,10 @@ namespace mmoe {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;   // producer, MMA 0, 4 epilogue warps, MMA 1
 constexpr int kSmemBudget = 227 * 1024 - 2048;   // dynamic shared memory we ask for at most (alignment slack excluded)
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kWaitHintNs = 200000;   // upper bound of one hardware-suspended barrier wait (the loop around it re-arms)
 
 struct UmmaParams {
   CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 128 rows
@@ -64,6 +67,12 @@ struct UmmaParams {
   float clamp;
   int fast_math;
   int has_shared_weights;
+  int num_stages;              // shared-memory pipeline depth in use (<= the compiled capacity)
+  int prefetch_ahead;          // K stages of weights requested from DRAM into L2 ahead of the pipeline (0 = off)
+  int ablate;                  // timing experiments only (results become meaningless): bit 0 skip weight-scale copies,
+                               // 1 token-scale copies, 2 token tiles, 3 tcgen05.cp, 4 MMAs, 5 weight tiles
+  CUtensorMap map_tok_routed_box[4];   // token maps with boxes of 16 / 32 / 64 / 128 rows
+  CUtensorMap map_tok_shared_box[4];
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -90,10 +99,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)     // the thread sleeps in hardware until the phase completes or the hint expires
       : "memory");
   return ok != 0;
 }
@@ -110,10 +119,37 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global [%0, {%1, %2, %3, %4, %5}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -161,9 +197,22 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t a_format, uint32_t n, ui
   return (sf_id << 4) | (a_format << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf_id << 29);
 }
 
+#ifndef MMOE_TRACE
+#define MMOE_TRACE 0
+#endif
+#if MMOE_TRACE
+#define TR_DECL(n) long long n = 0
+#define TR_T0() long long tr_t0 = clock64()
+#define TR_ADD(n) do { long long tr_t1 = clock64(); n += tr_t1 - tr_t0; tr_t0 = tr_t1; } while (0)
+#else
+#define TR_DECL(n)
+#define TR_T0()
+#define TR_ADD(n)
+#endif
+
 struct Control {          // lives at the start of shared memory
-  uint64_t full[16];
-  uint64_t empty[16];
+  uint64_t full[16];      // producer -> MMA warps: the stage's copies have landed
+  uint64_t empty[16];     // MMA -> producer: the stage's shared memory may be overwritten
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -175,11 +224,18 @@ struct Waiter {
   int32_t* status;
   uint64_t deadline;
   int kernel_id, role;
+  // whole-warp wait: one lane watches the barrier, the others sleep at the warp barrier (a polling warp would put 32
+  // requests on the barrier unit per probe and slow the producer and MMA threads that share it)
+  __device__ __forceinline__ bool wait_warp(uint32_t bar, uint32_t parity) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = wait(bar, parity);
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  }
   // true when the phase completed, false when the call is being abandoned
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
     for (uint32_t spin = 0;; ++spin) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((spin & 63u) == 63u) {
+      if ((spin & 3u) == 3u) {
         if (ctl->abort_flag != 0) return false;
         if (global_timer() > deadline) {
           ctl->abort_flag = 1;
@@ -195,20 +251,27 @@ struct Waiter {
   }
 };
 
+// Every task multiplies TWO 128-row weight tiles with one token tile: layer 1 the gate rows and the up rows of 128
+// channels, layer 2 two consecutive 128-row blocks of W2.  Two tiles per stage halve the per-byte cost of everything
+// that is paid per stage (barrier hand-offs, token tile, token scales) and give the two MMA-issuing warps one
+// accumulator each.
 template <int kLayer, int kBoxRows>
 struct Shape {
   static constexpr int kNCap = kBoxRows > kMaxTileTokens ? kMaxTileTokens : kBoxRows;   // accumulator columns per matrix
-  static constexpr int kATiles = kLayer == 1 ? 2 : 1;
-  static constexpr int kABytes = kATiles * kTileRows * kTileK;     // byte containers in shared memory
+  static constexpr int kABytes = 2 * kTileRows * kTileK;           // byte containers in shared memory
   static constexpr int kBBytes = kBoxRows * kTileK;
-  static constexpr int kSfBytes = (kATiles + 1) * 512;
+  // scale area of a stage: [A scales in tensor-memory order: 2 x 512][token scales 512][layer 1: raw 1024]
+  static constexpr int kSfBytes = 3 * 512 + (kLayer == 1 ? 1024 : 0);
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;   // control block + stages + alignment slack
-  static constexpr int kAccCols = kATiles * kNCap;                  // TMEM columns of one accumulator stage
-  static constexpr int kSfCol = 2 * kAccCols;                       // first TMEM column of the scale region
-  static_assert(kSfCol + 4 * (kATiles + 1) <= (int)kTmemCols, "TMEM budget");
+  static constexpr int kAccCols = 2 * kNCap;                        // TMEM columns of one accumulator stage
+  static constexpr int kSfCol = 2 * kAccCols;                       // scale region: A0, A1, token scales (one copy per MMA warp)
+  // K stages of the task's weights requested into L2 ahead of the shared-memory pipeline.  Measured on B200: any
+  // distance > 0 slows every token count down (the pipeline is not DRAM-latency bound), so the default is off.
+  static constexpr int kPrefetchAhead = 0;
+  static_assert(kSfCol + 16 <= (int)kTmemCols, "TMEM budget");
   static_assert(kStages >= 3, "pipeline too shallow");
 };
 
@@ -229,14 +292,15 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
   const int num_tiles = num_routed + (p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
   const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
   const int k_stages = p.k_dim / kTileK;
+  const uint32_t num_stages = static_cast<uint32_t>(p.num_stages);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S::kStages; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
-      mbar_init(smem_u32(&ctl->empty[i]), 1);
+      mbar_init(smem_u32(&ctl->empty[i]), 2);          // both MMA warps release a stage
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ctl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctl->tmem_full[i]), 2);      // both MMA warps finish an accumulator pair
       mbar_init(smem_u32(&ctl->tmem_empty[i]), 128);
     }
     ctl->abort_flag = 0;
@@ -257,86 +321,166 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------------ producer
+    // One thread.  Everything that does not change inside a task is computed once per task; the K loop only bumps
+    // 32-bit coordinates and two pointers, because a one-thread loop runs at instruction latency, not throughput.
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
+      const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+      const uint32_t a0 = smem_u32(a_base), b0 = smem_u32(b_base), sf0 = smem_u32(sf_base);
+      const int ab = p.ablate;
       bool ok = true;
+      TR_DECL(tr_wait); TR_DECL(tr_issue); TR_DECL(tr_iters); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
-        const Tile tile = pv.tiles[task / p.n_blocks];
-        const int nb = static_cast<int>(task % p.n_blocks);
+        const int tile_idx = static_cast<int>(task / p.n_blocks);
+        const int nb = static_cast<int>(task - (int64_t)tile_idx * p.n_blocks);
+        const Tile tile = pv.tiles[tile_idx];
         const bool shared = tile.expert == kSharedExpert;
+        // smallest token box that covers the tile (16 / 32 / 64 / 128 rows): fewer rows to move and to pad
+        const int n16 = (tile.n_valid + 15) & ~15;
+        int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : 3));
+        if ((16 << box_sel) > kBoxRows) box_sel = kBoxRows == 16 ? 0 : (kBoxRows == 32 ? 1 : (kBoxRows == 64 ? 2 : 3));
         const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
-        const CUtensorMap* tmap = shared ? &p.map_tok_shared : &p.map_tok_routed;
+        const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
         const int e = shared ? 0 : tile.expert;
-        // weight rows of this task inside expert e: [r_a, r_a+128) and, for layer 1, the up rows [r_b, r_b+128)
-        const int r_a = nb * kTileRows, r_b = p.inter + nb * kTileRows;
+        // The 256 stored weight rows of the task.  Layer 1 reads W13 in its stored order [g0..7, u0..7, g8..15, ...]
+        // through a 5-D map (K, row in group of 8, group of 16 rows, gate/up, slice): one box of 8 x 16 x 2 lands the
+        // 128 gate rows and then the 128 up rows of 128 consecutive channels.  Layer 2 reads 256 consecutive rows.
         const bool sliced = !shared && p.routed_sliced != 0;
-        const int half = p.rows_per_expert / 2;
-        const int row_a = sliced ? e * half + r_a % half : e * p.rows_per_expert + r_a;
-        const int slice_a = sliced ? r_a / half : 0;
-        const int row_b = sliced ? e * half + r_b % half : e * p.rows_per_expert + r_b;
-        const int slice_b = sliced ? r_b / half : 0;
-        const int32_t* wsf = (shared ? p.wsf_shared : p.wsf_routed) + (int64_t)e * k_stages * p.rows_per_expert;
-        const int32_t* tsf = shared ? p.tsf_shared : p.tsf_routed;
+        const int rows_slice = sliced ? p.rows_per_expert / 2 : p.rows_per_expert;   // rows of one expert in one slice
+        const int r0 = 2 * nb * kTileRows;                                           // first stored row of the task
+        const int slice = sliced ? r0 / rows_slice : 0;
+        const int row = e * rows_slice + r0 % rows_slice;
+        const int group = row / 16;
+        const int32_t* wsf = (shared ? p.wsf_shared : p.wsf_routed) + (int64_t)e * k_stages * p.rows_per_expert + r0;
         const int64_t tsf_rows = shared ? p.tsf_rows_shared : p.tsf_rows_routed;
-        const uint32_t a_tx = shared ? kTileRows * kTileK : kTileRows * kTileK / 2;   // packed FP4 counts its global bytes
-        const uint32_t tx = S::kATiles * a_tx + S::kBBytes + S::kSfBytes;
-        for (int kb = 0; kb < k_stages; ++kb) {
-          if (!waiter.wait(smem_u32(&ctl->empty[stage]), phase ^ 1u)) { ok = false; break; }
-          const uint32_t bar = smem_u32(&ctl->full[stage]);
-          mbar_expect_tx(bar, tx);
-          const uint32_t a_dst = smem_u32(a_base + stage * S::kABytes);
-          const uint32_t sf_dst = smem_u32(sf_base + stage * S::kSfBytes);
-          tma_load_3d(a_dst, wmap, kb * kTileK, row_a, slice_a, bar);
-          bulk_load(sf_dst, wsf + (int64_t)kb * p.rows_per_expert + r_a, 512, bar);
-          if (kLayer == 1) {
-            tma_load_3d(a_dst + kTileRows * kTileK, wmap, kb * kTileK, row_b, slice_b, bar);
-            bulk_load(sf_dst + 512, wsf + (int64_t)kb * p.rows_per_expert + r_b, 512, bar);
+        const int32_t* tsf = (shared ? p.tsf_shared : p.tsf_routed) + (int64_t)tile.sf_chunk * kChunkRows;
+        const uint32_t a_tx = shared ? 2 * kTileRows * kTileK : kTileRows * kTileK;   // packed FP4 counts its global bytes
+        uint32_t tx = 0;
+        if (!(ab & 32)) tx += a_tx;
+        if (!(ab & 4)) tx += (16u << box_sel) * kTileK;
+        if (!(ab & 1)) tx += 1024;
+        if (!(ab & 2)) tx += 512;
+        int k0 = 0;
+        for (int kb = 0; kb < k_stages; ++kb, k0 += kTileK, wsf += p.rows_per_expert, tsf += tsf_rows) {
+          TR_ADD(tr_issue);
+          if (!waiter.wait(empty0 + 8 * stage, phase ^ 1u)) { ok = false; break; }
+          TR_ADD(tr_wait);
+          const uint32_t bar = full0 + 8 * stage;
+          if (tx == 0) { mbar_arrive(bar); } else { mbar_expect_tx(bar, tx); }
+          const uint32_t a_dst = a0 + stage * S::kABytes;
+          const uint32_t sf_dst = sf0 + stage * S::kSfBytes;
+          if (!(ab & 32)) {
+            if (kLayer == 1) tma_load_5d(a_dst, wmap, k0, 0, group, 0, slice, bar);
+            else tma_load_3d(a_dst, wmap, k0, row, slice, bar);
+            // ask DRAM for a later K stage of this task now: it needs no shared memory, only L2
+            if (p.prefetch_ahead > 0 && kb + p.prefetch_ahead < k_stages) {
+              if (kLayer == 1) tma_prefetch_5d(wmap, k0 + p.prefetch_ahead * kTileK, 0, group, 0, slice);
+              else tma_prefetch_3d(wmap, k0 + p.prefetch_ahead * kTileK, row, slice);
+            }
           }
-          tma_load_2d(smem_u32(b_base + stage * S::kBBytes), tmap, kb * kTileK, tile.row0, bar);
-          bulk_load(sf_dst + S::kATiles * 512, tsf + (int64_t)kb * tsf_rows + (int64_t)tile.sf_chunk * kChunkRows, 512, bar);
-          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+          // layer 1: raw scales of the 256 stored rows, permuted by warp 6; layer 2: two chunks already in order
+          if (!(ab & 1)) bulk_load(sf_dst + (kLayer == 1 ? 3 * 512 : 0), wsf, 1024, bar);
+          if (!(ab & 4)) tma_load_2d(b0 + stage * S::kBBytes, tmap, k0, tile.row0, bar);
+          if (!(ab & 2)) bulk_load(sf_dst + 2 * 512, tsf, 512, bar);
+          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+#if MMOE_TRACE
+          ++tr_iters;
+#endif
         }
       }
+#if MMOE_TRACE
+      TR_ADD(tr_issue);
+      if (blockIdx.x == 0) printf("L%d producer: iters %lld wait_empty %lld issue %lld\n", kLayer, tr_iters, tr_wait, tr_issue);
+#endif
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 6) {
+    // ------------------------------------------------------------------------------------------------ MMA issuers
+    // Two warps, one per weight tile / accumulator (h = 0, 1).  The whole warp walks the loop so that loop state
+    // stays warp-uniform; one elected lane issues.  Each warp copies the scales it needs into its own TMEM columns,
+    // so no ordering between the two warps' tensor-core instructions is needed.
+    // Layer 1 first rearranges its tile's weight scales: the stored W13 scales follow the stored row order (gate/up
+    // interleaved by 8, then the 4x32 transpose inside each 128-row block), the accumulator wants the scales of 128
+    // gate (h = 0) or up (h = 1) channels in tensor-memory order; each lane moves 4 of the 128 words.
+    {
+      const int h = warp == 1 ? 0 : 1;
       uint32_t stage = 0, phase = 0;
       uint32_t it = 0;
       bool ok = true;
+      const uint32_t ready0 = smem_u32(&ctl->full[0]);
+      const uint32_t empty0 = smem_u32(&ctl->empty[0]);
+      const uint64_t sw128_hi = (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+      const uint64_t sf_hi = (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
+      const uint32_t a_lo0 = ((smem_u32(a_base) & 0x3FFFFu) >> 4) + h * (kTileRows * kTileK >> 4);
+      const uint32_t b_lo0 = (smem_u32(b_base) & 0x3FFFFu) >> 4;
+      const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
+      const uint32_t sfa_col = tmem_base + S::kSfCol + 4 * h;
+      const uint32_t sfb_col = tmem_base + S::kSfCol + 8 + 4 * h;
+      const int ab = p.ablate;
+      int src[4];                                    // layer 1: source word of the 4 destination words this lane writes
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int q = lane + 32 * t;                 // destination position inside the 128-word block
+        const int m = 32 * (q & 3) + (q >> 2);       // channel of the tile that position serves
+        const int r = 16 * ((m & 63) >> 3) + 8 * h + (m & 7);   // stored row inside its 128-row block
+        src[t] = 128 * (m >> 6) + 4 * (r & 31) + (r >> 5);
+      }
+      TR_DECL(tr_wte); TR_DECL(tr_wfull); TR_DECL(tr_issue); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
         const Tile tile = pv.tiles[task / p.n_blocks];
         const bool shared = tile.expert == kSharedExpert;
         const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
-        if (!waiter.wait(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
+        TR_ADD(tr_issue);
+        if (!waiter.wait_warp(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
+        TR_ADD(tr_wte);
         tc_fence_after();
         const uint32_t n = static_cast<uint32_t>((tile.n_valid + 15) & ~15);
-        const uint32_t a_format = shared ? 0u : 5u;
-        const uint32_t d0 = tmem_base + acc_stage * S::kAccCols;
-        const uint32_t sf_col = tmem_base + S::kSfCol;
+        const uint32_t idesc0 = make_idesc(shared ? 0u : 5u, n, 0);
+        const uint32_t d = tmem_base + acc_stage * S::kAccCols + h * S::kNCap;
+        const uint32_t sfb = sfb_col + tile.sf_col;
         for (int kb = 0; kb < k_stages; ++kb) {
-          if (!waiter.wait(smem_u32(&ctl->full[stage]), phase)) { ok = false; break; }
+          TR_ADD(tr_issue);
+          if (!waiter.wait_warp(ready0 + 8 * stage, phase)) { ok = false; break; }
+          TR_ADD(tr_wfull);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(a_base + stage * S::kABytes);
-          const uint32_t b_addr = smem_u32(b_base + stage * S::kBBytes);
-          const uint32_t sf_addr = smem_u32(sf_base + stage * S::kSfBytes);
+          const uint32_t a_lo = a_lo0 + stage * (S::kABytes >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (S::kBBytes >> 4);
+          const uint32_t sf_lo = sf_lo0 + stage * (S::kSfBytes >> 4);
+          if (kLayer == 1) {
+            uint32_t* out = reinterpret_cast<uint32_t*>(sf_base + stage * S::kSfBytes) + 128 * h;
+            const uint32_t* in = reinterpret_cast<const uint32_t*>(sf_base + stage * S::kSfBytes) + 3 * 128;
+            uint32_t v[4];
 #pragma unroll
-          for (int i = 0; i <= S::kATiles; ++i) tc_cp_sf(sf_col + 4 * i, smem_desc_sf(sf_addr + 512 * i));
-          const uint32_t sfb = sf_col + 4 * S::kATiles + tile.sf_col;
+            for (int t = 0; t < 4; ++t) v[t] = in[src[t]];
 #pragma unroll
-          for (int k = 0; k < kTileK / 32; ++k) {
-            const uint32_t idesc = make_idesc(a_format, n, k);
-            const uint64_t bdesc = smem_desc_sw128(b_addr + k * 32);
-            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-            tc_mma(d0, smem_desc_sw128(a_addr + k * 32), bdesc, idesc, sf_col, sfb, acc);
-            if (kLayer == 1)
-              tc_mma(d0 + S::kNCap, smem_desc_sw128(a_addr + kTileRows * kTileK + k * 32), bdesc, idesc, sf_col + 4, sfb, acc);
+            for (int t = 0; t < 4; ++t) out[lane + 32 * t] = v[t];
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to tcgen05.cp
+            __syncwarp();
           }
-          tc_commit(smem_u32(&ctl->empty[stage]));      // shared memory of this stage is free once these MMAs retire
-          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+          if (elect_one()) {
+            if (!(ab & 8)) {
+              tc_cp_sf(sfa_col, sf_hi | (sf_lo + 32 * h));
+              tc_cp_sf(sfb_col, sf_hi | (sf_lo + 64));
+            }
+            if (!(ab & 16)) {
+#pragma unroll
+              for (int k = 0; k < kTileK / 32; ++k)
+                tc_mma(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
+                       idesc0 + k * ((1u << 4) | (1u << 29)),               // scale byte k of both operands
+                       sfa_col, sfb, (kb | k) != 0 ? 1u : 0u);
+            }
+            if (ab & 64) mbar_arrive(empty0 + 8 * stage);
+            else tc_commit(empty0 + 8 * stage);       // shared memory of this stage is free once these MMAs retire
+          }
+          __syncwarp();
+          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(smem_u32(&ctl->tmem_full[acc_stage]));
+        if (ok && elect_one()) tc_commit(smem_u32(&ctl->tmem_full[acc_stage]));
+        __syncwarp();
       }
+#if MMOE_TRACE
+      TR_ADD(tr_issue);
+      if (blockIdx.x == 0 && lane == 0) printf("L%d mma%d: tasks %u wait_tmem_empty %lld wait_full %lld issue %lld\n", kLayer, h, it, tr_wte, tr_wfull, tr_issue);
+#endif
     }
   } else {
     // ------------------------------------------------------------------------------------------------ epilogue
@@ -344,55 +488,78 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     uint32_t it = 0;
     bool ok = true;
+    TR_DECL(tr_wfull); TR_DECL(tr_work); TR_T0();
     for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
       const Tile tile = pv.tiles[task / p.n_blocks];
       const int nb = static_cast<int>(task % p.n_blocks);
       const bool shared = tile.expert == kSharedExpert;
       const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
-      if (!waiter.wait(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { ok = false; break; }
+      // Per-token side data of the tile (top-k weight / destination row), one coalesced load per 32 tokens issued
+      // before the accumulator is awaited; tokens read it by shuffle.
+      float wv[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+      int dv[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = 32 * c + lane;
+        if (i < tile.n_valid) {
+          if (kLayer == 1) { if (!shared) wv[c] = __ldg(p.pool_w + tile.row0 + i); }
+          else dv[c] = shared ? tile.row0 + i : __ldg(p.pool_dst + tile.row0 + i);
+        }
+      }
+      TR_ADD(tr_work);
+      if (!waiter.wait_warp(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { ok = false; break; }
+      TR_ADD(tr_wfull);
       tc_fence_after();
       const uint32_t d0 = tmem_base + lane_sel + acc_stage * S::kAccCols;
       const int n16 = (tile.n_valid + 15) & ~15;
-      const int row = nb * kTileRows + q * 32 + lane;       // channel (layer 1) or output feature (layer 2)
       if (kLayer == 1) {
+        const int row = nb * kTileRows + q * 32 + lane;       // channel
         uint8_t* act = shared ? p.act_shared : p.act_routed;
         uint8_t* act_sf = shared ? p.act_sf_shared : p.act_sf_routed;
         const int64_t sf_rows = shared ? p.act_sf_rows_shared : p.act_sf_rows_routed;
         // scale byte of (token i, channel group nb*4+q): word nb of the chunk row, byte q
         uint8_t* sf_out = act_sf + ((int64_t)nb * sf_rows + (int64_t)tile.sf_chunk * kChunkRows) * 4 + q;
+        uint8_t* act_col = act + (int64_t)tile.row0 * p.inter + row;
         for (int i0 = 0; i0 < n16; i0 += 16) {
           uint32_t g[16], u[16];
           tc_ld16(d0 + i0, g);
           tc_ld16(d0 + S::kNCap + i0, u);
           tc_ld_wait();
+          const int c = i0 >> 5;
+          const float wcur = c == 0 ? wv[0] : (c == 1 ? wv[1] : (c == 2 ? wv[2] : wv[3]));
           int my_sf = 0;
+          // branch-free over the 16 columns so that their dependency chains interleave; padding columns compute
+          // garbage that is never stored
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int i = i0 + j;
-            if (i < tile.n_valid) {       // uniform across the warp
-              const float wt = shared ? 1.0f : __ldg(p.pool_w + tile.row0 + i);
-              const float a = swiglu_act(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp, p.fast_math != 0);
-              const float amax = warp_max_nonneg(fabsf(a));
-              const int sf_exp = ue8m0_exp_of_amax(amax);
-              act[(int64_t)(tile.row0 + i) * p.inter + row] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
-              if (lane == j) my_sf = sf_exp;
-            }
+            const float wt = __shfl_sync(0xffffffffu, wcur, (i0 & 16) + j);
+            const float a = swiglu_act(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp, p.fast_math != 0);
+            const float amax = warp_max_nonneg(fabsf(a));
+            const int sf_exp = ue8m0_exp_of_amax(amax);
+            g[j] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
+            if (lane == j) my_sf = sf_exp;
           }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (i0 + j < tile.n_valid) act_col[(int64_t)(i0 + j) * p.inter] = static_cast<uint8_t>(g[j]);
           if (lane < 16 && i0 + lane < tile.n_valid)
             sf_out[chunk_pos(tile.sf_col * 32 + i0 + lane) * 4] = static_cast<uint8_t>(my_sf);
         }
       } else {
-        __nv_bfloat16* out = shared ? p.shared_out : p.ret;
-        for (int i0 = 0; i0 < n16; i0 += 16) {
-          uint32_t v[16];
-          tc_ld16(d0 + i0, v);
-          tc_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int i = i0 + j;
-            if (i < tile.n_valid) {
-              const int64_t dst = shared ? (int64_t)(tile.row0 + i) : (int64_t)__ldg(p.pool_dst + tile.row0 + i);
-              out[dst * p.hidden + row] = __float2bfloat16_rn(__uint_as_float(v[j]));
+        for (int h = 0; h < 2; ++h) {
+          const int row = nb * 2 * kTileRows + h * kTileRows + q * 32 + lane;     // output feature
+          __nv_bfloat16* out = (shared ? p.shared_out : p.ret) + row;
+          for (int i0 = 0; i0 < n16; i0 += 16) {
+            uint32_t v[16];
+            tc_ld16(d0 + h * S::kNCap + i0, v);
+            tc_ld_wait();
+            const int c = i0 >> 5;
+            const int dcur = c == 0 ? dv[0] : (c == 1 ? dv[1] : (c == 2 ? dv[2] : dv[3]));
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int dst = __shfl_sync(0xffffffffu, dcur, (i0 & 16) + j);
+              if (i0 + j < tile.n_valid) out[(int64_t)dst * p.hidden] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
           }
         }
@@ -400,6 +567,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->tmem_empty[acc_stage]));
     }
+#if MMOE_TRACE
+    TR_ADD(tr_work);
+    if (blockIdx.x == 0 && threadIdx.x == 64) printf("L%d epilogue: tasks %u wait_tmem_full %lld work %lld\n", kLayer, it, tr_wfull, tr_work);
+#endif
   }
 
   // ---------------------------------------------------------------------------------------------------- teardown
@@ -425,6 +596,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 int g_num_sms = 0;
+int g_tune_prefetch = -1;   // < 0: the compiled default of each kernel
+int g_tune_stages = 0;      // 0: every stage that fits
+int g_tune_ablate = 0;
 
 // token rows: 2-D map [rows, K] of E4M3 bytes
 int make_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows, uint32_t box_rows,
@@ -449,9 +623,27 @@ int make_weight_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_ele
   const uint64_t rows = rows_total / slices;
   const cuuint64_t dims[3] = {k_elems, rows, slices};
   const cuuint64_t strides[2] = {row_bytes, slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes};
-  const cuuint32_t box[3] = {kTileK, kTileRows, 1};
+  const cuuint32_t box[3] = {kTileK, 2 * kTileRows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+// W13 (stored rows [g0..7, u0..7, g8..15, ...]): 5-D map [slices, gate/up, groups of 16 rows, row in group of 8, K];
+// a box of 8 x 16 x 2 is the 128 gate rows followed by the 128 up rows of 128 channels
+int make_w13_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows_total, int64_t slice_stride) {
+  const uint64_t row_bytes = fp4 ? k_elems / 2 : k_elems;
+  const uint64_t slices = slice_stride > 0 ? 2 : 1;
+  const uint64_t rows = rows_total / slices;
+  const cuuint64_t dims[5] = {k_elems, 8, rows / 16, 2, slices};
+  const cuuint64_t strides[4] = {row_bytes, 16 * row_bytes, 8 * row_bytes,
+                                 slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes};
+  const cuuint32_t box[5] = {kTileK, 8, 16, 2, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 5,
                               const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -465,8 +657,13 @@ cudaError_t prepare_one() {
 }
 
 template <int kLayer, int kBoxRows>
-cudaError_t launch_one(const UmmaParams& p, cudaStream_t s) {
-  umma_kernel<kLayer, kBoxRows><<<g_num_sms, kThreads, Shape<kLayer, kBoxRows>::kSmemBytes, s>>>(p);
+cudaError_t launch_one(const UmmaParams& p0, cudaStream_t s) {
+  using S = Shape<kLayer, kBoxRows>;
+  UmmaParams p = p0;
+  p.num_stages = g_tune_stages > 0 && g_tune_stages < S::kStages ? g_tune_stages : S::kStages;
+  p.prefetch_ahead = g_tune_prefetch >= 0 ? g_tune_prefetch : S::kPrefetchAhead;
+  p.ablate = g_tune_ablate;
+  umma_kernel<kLayer, kBoxRows><<<g_num_sms, kThreads, S::kSmemBytes, s>>>(p);
   return cudaGetLastError();
 }
 
@@ -483,6 +680,12 @@ cudaError_t launch_layer(const UmmaParams& p, int box, cudaStream_t s) {
 }
 
 }  // namespace
+
+void set_tuning(int prefetch_ahead, int max_stages) {
+  g_tune_prefetch = prefetch_ahead;
+  g_tune_stages = max_stages & 0xFFFF;
+  g_tune_ablate = max_stages >> 16;       // experiments only: high half-word = ablation mask
+}
 
 int prepare_umma(const MmoeGeometry& geo) {
   (void)geo;
@@ -519,14 +722,19 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
 
   UmmaParams p1{};
   int bad = 0;
-  bad |= make_weight_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
+  bad |= make_w13_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
   bad |= make_map(&p1.map_tok_routed, false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, box, false);
   if (has_shared) {
-    bad |= make_weight_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
+    bad |= make_w13_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
     bad |= make_map(&p1.map_tok_shared, false, c.ws + c.lay.x, h, c.geo.num_max_tokens, box, false);
   } else {
     p1.map_w_shared = p1.map_w_routed;
     p1.map_tok_shared = p1.map_tok_routed;
+  }
+  for (int b = 0; b < 4; ++b) {
+    bad |= make_map(&p1.map_tok_routed_box[b], false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, 16u << b, false);
+    if (has_shared) bad |= make_map(&p1.map_tok_shared_box[b], false, c.ws + c.lay.x, h, c.geo.num_max_tokens, 16u << b, false);
+    else p1.map_tok_shared_box[b] = p1.map_tok_routed_box[b];
   }
   if (bad) return cudaErrorInvalidValue;
   p1.plan = c.ws + c.lay.plan;
@@ -567,6 +775,11 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
     p2.map_w_shared = p2.map_w_routed;
     p2.map_tok_shared = p2.map_tok_routed;
   }
+  for (int b = 0; b < 4; ++b) {
+    bad |= make_map(&p2.map_tok_routed_box[b], false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, 16u << b, false);
+    if (has_shared) bad |= make_map(&p2.map_tok_shared_box[b], false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, 16u << b, false);
+    else p2.map_tok_shared_box[b] = p2.map_tok_routed_box[b];
+  }
   if (bad) return cudaErrorInvalidValue;
   p2.wsf_routed = static_cast<const int32_t*>(w.w2_sf);
   p2.wsf_shared = static_cast<const int32_t*>(w.shared_w2_sf);
@@ -578,7 +791,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p2.k_dim = inter;
   p2.rows_per_expert = h;
   p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
-  p2.n_blocks = h / kTileRows;
+  p2.n_blocks = h / (2 * kTileRows);
 
   const int mask = o.layer_mask == 0 ? 3 : o.layer_mask;
   cudaError_t e = cudaSuccess;
