@@ -145,3 +145,90 @@ def test_full_size_engines_agree_and_permutation_invariance():
     assert_parity(y_tc, y_sc.cpu(), "tensor-core vs scalar engine, E=384")
     perm = torch.randperm(m, generator=torch.Generator().manual_seed(1)).cuda()
     assert torch.equal(run(hid[perm], ids[perm], w[perm], 0), y_tc[perm])
+
+
+def test_layer_class_loads_a_checkpoint_and_runs(monkeypatch):
+    """The plugin layer class end to end: checkpoint shards (w1 / w3 / w2 + scales) through ``weight_loader`` into the
+    two-slice parameters, ``forward`` through the real backend, reload in place, output against the oracle."""
+    from types import SimpleNamespace
+    from vllm_plugin_b200 import _standin, api
+    from vllm_plugin_b200.experts import make_experts_class
+
+    layer_def = H.make_layer(shared=True, seed=21, **SMALL)
+    h, i, e, k = layer_def.hidden, layer_def.inter, layer_def.num_experts, layer_def.num_topk
+    backend = SimpleNamespace(**{name: getattr(api, name) for name in api.__all__ if name != "SymmBuffer"})
+    backend.get_unsupported_reason_for_mega_moe = (
+        lambda *a, **kw: api.get_unsupported_reason_for_mega_moe(*a, **{**kw, "allow_unvalidated": True}))
+    cls = make_experts_class(_standin.DeepGemmMegaMoEExperts, _standin.get_ep_group, _standin.MEGA_MOE_MXFP4)
+    monkeypatch.setattr(cls, "_import_backend", staticmethod(lambda: backend))
+    cfg = SimpleNamespace(parallel_config=SimpleNamespace(enable_eplb=False),
+                          scheduler_config=SimpleNamespace(max_num_batched_tokens=256))
+    sh = layer_def.shared
+    shared_mlp = SimpleNamespace(
+        gate_up_proj=SimpleNamespace(weight=sh.w13.cuda(), weight_scale=sh.w13_sf.cuda()),
+        down_proj=SimpleNamespace(weight=sh.w2.cuda(), weight_scale=sh.w2_sf.cuda()))
+    mod = cls(cfg, prefix="model.layers.0.experts", num_experts=e, num_local_experts=e, experts_start_idx=0, top_k=k,
+              hidden_size=h, intermediate_size=i, weight_format=_standin.MEGA_MOE_MXFP4,
+              activation=_standin.MegaMoEActivation(clamp=10.0), shared_experts=shared_mlp, device="cuda")
+    ptrs = [p.data_ptr() for p in mod.parameters()]
+
+    def load(experts):
+        for ex, ew in enumerate(experts):
+            for shard, w, s in (("w1", ew.w13[:i], ew.w13_sf[:i]), ("w3", ew.w13[i:], ew.w13_sf[i:]), ("w2", ew.w2, ew.w2_sf)):
+                prefix = "w2" if shard == "w2" else "w13"
+                assert mod.weight_loader(getattr(mod, f"{prefix}_weight"), w.cuda(), f"experts.{prefix}_weight", shard, ex, True)
+                assert mod.weight_loader(getattr(mod, f"{prefix}_weight_scale"), s.cuda(), f"experts.{prefix}_weight_scale", shard, ex, True)
+
+    load(layer_def.experts)
+    m = 50
+    hid = O.make_hidden(m, h, 1)
+    ids, w = O.make_routing(m, e, k, 2)
+    y = mod(hid.cuda(), w.cuda(), ids.cuda())
+    assert_parity(y, H.oracle_layer(layer_def, hid, ids, w), "layer class")
+    # reload other weights into the same parameters: addresses unchanged, outputs follow the new weights
+    layer2 = H.make_layer(shared=True, seed=22, **SMALL)
+    layer2.shared = layer_def.shared
+    load(layer2.experts)
+    assert [p.data_ptr() for p in mod.parameters()] == ptrs
+    y2 = mod(hid.cuda(), w.cuda(), ids.cuda())
+    assert_parity(y2, H.oracle_layer(layer2, hid, ids, w), "layer class after reload")
+
+
+def test_cuda_graph_replay_of_every_variant():
+    """Every BLOCK_M variant is prepared before capture; a captured call replays bit-identically and follows new inputs
+    staged into the same buffers."""
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend.workspace import SingleRankGroup
+    layer = H.make_layer(shared=True, seed=31, **SMALL)
+    dev = torch.device("cuda", 0)
+    l1, l2, sl1, sl2 = H.kernel_weights(layer, dev)
+    buf = api.get_symm_buffer_for_mega_moe(SingleRankGroup(), layer.num_experts, 1920, layer.num_topk, layer.hidden, layer.inter, 1)
+    variants = api.precompile_mega_moe_variants(1, layer.num_experts, 1920, layer.num_topk, layer.hidden, layer.inter, 1)
+    assert variants == (16, 32, 64, 128, 192, 240)
+    for m in (1, 40, 130, 700, 1900):
+        hid_a, hid_b = O.make_hidden(m, layer.hidden, m), O.make_hidden(m, layer.hidden, m + 1)
+        ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, m)
+        x = hid_a.cuda()
+        ids_d, w_d = ids.cuda(), w.cuda()
+        y = torch.empty((m, layer.hidden), dtype=torch.bfloat16, device=dev)
+
+        def call():
+            api.stage_inputs_for_mega_moe(buf, x, ids_d, w_d)
+            api.fp8_fp4_mega_moe(y, l1, l2, buf, sl1, sl2, activation_clamp=10.0)
+
+        call()
+        eager = y.clone()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call()
+        y.zero_()
+        g.replay()
+        assert torch.equal(y, eager), m
+        x.copy_(hid_b.cuda())
+        g.replay()
+        assert_parity(y, H.oracle_layer(layer, hid_b, ids, w), f"graph replay m={m}")
