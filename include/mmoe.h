@@ -136,6 +136,23 @@ typedef struct MmoeOptions {
 
 /* Count this rank's routes per destination expert and order them (send order = by expert, token, slot). */
 int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream);
+/* No counterpart in the reference.  Same result as the route-ordering step of `mmoe_dispatch_count`, for callers that
+ * cannot let this library touch the device allocator on their behalf: a serving process that has already handed all
+ * free device memory to its own pool (a late allocation fails or fragments it), or a latency-critical loop that cannot
+ * afford the device-wide synchronisation cudaMalloc / cudaFree imply.  The caller passes the input (`topk_idx`, int64
+ * [num_tokens, num_topk], -1 = masked route; ids >= num_experts are treated as masked) and the four outputs
+ * (`send_count` int32 [num_experts], `send_offset` int32 [num_experts+1], `route_pos` and `sorted_route` int32
+ * [num_tokens*num_topk]); the per-chunk counts the passes need live in a 64 KB array built into the library image,
+ * which every GPU that loads the library keeps until the process exits.  Limits: num_tokens <= 4096 and
+ * num_experts <= 512; larger sizes are rejected with MMOE_ERR_INVALID_ARGUMENT.  This function calls no cudaMalloc,
+ * cudaFree or other allocating routine.  The first call on a device looks up the array's device address (the device
+ * must be current); make that first call before any stream capture.  All calls on a device share the one array: it
+ * needs no clearing (every cell read is written first within the call), but two calls that overlap on the GPU (for
+ * example on different streams) race on it. */
+int mmoe_route_order_noalloc(const int64_t* topk_idx, int32_t num_tokens, int32_t num_topk, int32_t num_experts,
+                             int32_t* send_count, int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route,
+                             void* stream);
+
 /* EP>1: gather rows, scales and weights into send order. */
 int mmoe_dispatch_pack(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream);
 /* Build the pool plan from `recv_count`, place received rows into the BLOCK_M-aligned pool, add the per-expert totals

@@ -28,7 +28,7 @@ ENGINE_SCALAR_VALIDATION = 1
 EXPORTED_SYMBOLS = (
     "mmoe_layout", "mmoe_block_m", "mmoe_prepare", "mmoe_stage_inputs", "mmoe_dispatch_count", "mmoe_dispatch_pack",
     "mmoe_dispatch_place", "mmoe_experts", "mmoe_combine", "mmoe_forward", "mmoe_read_status", "mmoe_status_string",
-    "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning",
+    "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc",
 )
 
 
@@ -96,6 +96,7 @@ def load() -> ctypes.CDLL:
     lib.mmoe_last_error.restype = ctypes.c_char_p
     lib.mmoe_abi_version.argtypes = []
     lib.mmoe_set_tuning.argtypes = [i32, i32]
+    lib.mmoe_route_order_noalloc.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
     for name in EXPORTED_SYMBOLS:
         fn = getattr(lib, name)
         if fn.restype is not ctypes.c_char_p:

@@ -260,6 +260,22 @@ int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_to
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_count launch");
 }
 
+int mmoe_route_order_noalloc(const int64_t* topk_idx, int32_t num_tokens, int32_t num_topk, int32_t num_experts,
+                             int32_t* send_count, int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route,
+                             void* stream) {
+  const int max_t = mmoe::route_order_static_max_tokens(), max_e = mmoe::route_order_static_max_experts();
+  if (num_tokens < 0 || num_tokens > max_t)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "num_tokens=%d exceeds the built-in scratch of mmoe_route_order_noalloc (at most %d tokens)", num_tokens, max_t);
+  if (num_experts < 1 || num_experts > max_e)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "num_experts=%d exceeds the built-in scratch of mmoe_route_order_noalloc (at most %d experts)", num_experts, max_e);
+  if (num_topk < 1 || num_topk > 31) return fail(MMOE_ERR_INVALID_ARGUMENT, "num_topk=%d outside [1, 31]", num_topk);
+  if (send_count == nullptr || send_offset == nullptr || (num_tokens > 0 && (topk_idx == nullptr || route_pos == nullptr || sorted_route == nullptr)))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "mmoe_route_order_noalloc: input and output pointers must not be NULL");
+  cudaError_t e = mmoe::route_order_static(topk_idx, num_tokens, num_topk, num_experts, send_count, send_offset, route_pos,
+                                           sorted_route, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "route_order_noalloc");
+}
+
 int mmoe_dispatch_pack(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);

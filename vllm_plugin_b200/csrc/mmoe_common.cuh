@@ -172,5 +172,9 @@ cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOp
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 int prepare_umma(const MmoeGeometry& geo);   // returns an MMOE_* code
 void set_tuning(int prefetch_ahead, int max_stages);
+cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_experts, int32_t* send_count,
+                               int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route, cudaStream_t s);
+int route_order_static_max_tokens();
+int route_order_static_max_experts();
 
 }  // namespace mmoe

@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_local_kernel(
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     int64_t id = topk_idx[r0 + i];
-    if (id >= num_experts) { report_bad_index(status); id = -1; }
+    if (id >= num_experts) { if (status != nullptr) report_bad_index(status); id = -1; }
     ids[i] = id < 0 ? -1 : static_cast<int32_t>(id);
   }
   __syncthreads();
@@ -196,6 +196,51 @@ cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s) {
   }
   return cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Route ordering without any allocation.  The per-chunk expert counts, the only scratch the three passes need, live in
+// a file-scope device array: every GPU that loads this library holds these 64 KB until the process exits.  Host code
+// may only use the array's *address*, obtained once per device with cudaGetSymbolAddress while that device is current
+// (the bare symbol name is a host-side stand-in, not a device pointer).
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kStaticMaxTokens = 4096;                                   // 32 chunks of 128 tokens
+constexpr int kStaticMaxExperts = 512;
+constexpr int kStaticScratchInts = (kStaticMaxTokens / kSortChunkTokens) * kStaticMaxExperts;
+static __device__ __align__(256) int32_t g_route_order_scratch[kStaticScratchInts];
+
+namespace {
+constexpr int kMaxDevices = 64;
+int32_t* g_scratch_ptr[kMaxDevices] = {};
+}
+
+cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_experts, int32_t* send_count,
+                               int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route, cudaStream_t s) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (g_scratch_ptr[dev] == nullptr) {           // set-up: first call on this device
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_route_order_scratch);
+    if (e != cudaSuccess) return e;
+    g_scratch_ptr[dev] = static_cast<int32_t*>(ptr);
+  }
+  int32_t* chunk_count = g_scratch_ptr[dev];
+  // nothing in the scratch has to start at zero: pass A overwrites every (chunk, expert) cell that passes B and C read
+  const int chunks = std::max(1, (m + kSortChunkTokens - 1) / kSortChunkTokens);
+  const size_t smem = (size_t)(kSortChunkTokens * k + num_experts) * sizeof(int32_t);
+  sort_local_kernel<<<chunks, kSortThreads, smem, s>>>(topk_idx, route_pos, chunk_count, nullptr, m, k, num_experts);
+  sort_scan_kernel<<<1, 1024, 0, s>>>(chunk_count, send_count, send_offset, nullptr, chunks, num_experts);
+  if (m > 0) {
+    const int blocks = static_cast<int>(std::min<int64_t>(((int64_t)m * k + kSortThreads - 1) / kSortThreads, 148 * 8));
+    sort_place_kernel<<<blocks, kSortThreads, 0, s>>>(topk_idx, chunk_count, send_offset, route_pos, sorted_route, m, k,
+                                                      num_experts);
+  }
+  return cudaGetLastError();
+}
+
+int route_order_static_max_tokens() { return kStaticMaxTokens; }
+int route_order_static_max_experts() { return kStaticMaxExperts; }
 
 // =====================================================================================================================
 // EP > 1: gather the rows, scale words and weights of this rank's routes into send order (sorted by destination
