@@ -1,0 +1,146 @@
+"""Multi-rank harness shared by the CPU (gloo) and GPU (NCCL) expert-parallel tests: one process per rank, spawned with
+torch.multiprocessing, rendezvous on 127.0.0.1."""
+
+from __future__ import annotations
+
+import os
+import socket
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, backend, port, fn, args, errors):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    try:
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+        fn(rank, world, *args)
+        dist.barrier()
+    except Exception:  # noqa: BLE001
+        errors.put((rank, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_ranks(world: int, backend: str, fn, *args, timeout: float = 600.0) -> None:
+    ctx = mp.get_context("spawn")
+    errors = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, backend, port, fn, args, errors)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()                      # the exact processes started above
+    msgs = []
+    while not errors.empty():
+        msgs.append("rank %d:\n%s" % errors.get())
+    assert not hung, "ranks did not finish"
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# rank bodies (module level so that spawn can pickle them)
+# ---------------------------------------------------------------------------------------------------------------------
+def exchange_body(rank, world, num_experts, k, tokens_per_rank, seed):
+    """Host logic of the EP exchanges on CPU tensors: what each rank receives and in which order, and that the return
+    exchange puts every row back where its route expects it."""
+    from oracle import mmoe_oracle as O
+    from vllm_plugin_b200.backend import frontend as F
+
+    group = dist.group.WORLD
+    e_l = num_experts // world
+    ids_all = [O.make_routing(tokens_per_rank[r], num_experts, k, seed + r, zipf_s=1.2, mask_frac=0.1)[0] for r in range(world)]
+    ids = ids_all[rank]
+    m = ids.shape[0]
+    # what mmoe_dispatch_count / mmoe_dispatch_pack produce: routes sorted by (expert, token, slot)
+    flat = ids.reshape(-1)
+    routes = sorted((int(flat[i]), i) for i in range(flat.numel()) if int(flat[i]) >= 0)
+    send_count = torch.bincount(torch.tensor([e for e, _ in routes], dtype=torch.int64), minlength=num_experts).to(torch.int32)
+    recv_count = torch.zeros((world, e_l), dtype=torch.int32)
+    send_splits, recv_splits = F.exchange_counts(group, send_count, recv_count)
+    plan = O.dispatch_plan(ids_all, num_experts, rank, 16)
+    assert torch.equal(recv_count.long(), plan.recv_count)                      # bit-exact receive counts
+    assert send_splits == [int(send_count[r * e_l:(r + 1) * e_l].sum()) for r in range(world)]
+    # rows carry (source rank, route id) so that the order can be checked after the exchange
+    send_rows = torch.tensor([[rank, i] for _, i in routes], dtype=torch.int32).reshape(-1, 2)
+    recv_rows = torch.full((int(sum(recv_splits)) + 3, 2), -1, dtype=torch.int32)
+    F.exchange_rows(group, recv_rows, send_rows, recv_splits, send_splits)
+    lo = rank * e_l
+    want = []
+    for src in range(world):                                                     # receive order: source, expert, token, slot
+        f = ids_all[src].reshape(-1)
+        want += [[src, i] for e, i in sorted((int(f[i]), i) for i in range(f.numel()) if lo <= int(f[i]) < lo + e_l)]
+    assert recv_rows[: len(want)].tolist() == want
+    assert bool((recv_rows[len(want):] == -1).all())
+    # per-expert pool = concatenation over sources, which is the oracle's (source, token, slot) order
+    k_ = ids.shape[1]
+    for ex in range(e_l):
+        got = [(s, i // k_, i % k_) for s, i in want if int(ids_all[s].reshape(-1)[i]) == lo + ex]
+        assert sorted(got) == plan.routes[ex] and got == plan.routes[ex]
+    # return path: every rank sends back what it received; rows come home in the sender's own send order
+    back = torch.full((len(routes) + 2, 2), -1, dtype=torch.int32)
+    F.exchange_rows(group, back, recv_rows, send_splits, recv_splits)
+    assert torch.equal(back[: len(routes)], send_rows)
+
+
+def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max):
+    """Whole layer at EP = world on GPUs: per-rank output against the oracle, receive counts and statistics bit-exact."""
+    import helpers as H
+    from oracle import mmoe_oracle as O
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend.frontend import read_status
+
+    dev = torch.device("cuda", rank)
+    layer = H.make_layer(seed=seed, **geometry)
+    e, k = layer.num_experts, layer.num_topk
+    e_l = e // world
+    hid = [O.make_hidden(tokens_per_rank[r], layer.hidden, seed + 10 + r) for r in range(world)]
+    routing = [O.make_routing(tokens_per_rank[r], e, k, seed + 20 + r, **routing_kw) for r in range(world)]
+    ids = [r_[0] for r_ in routing]
+    w = [r_[1] for r_ in routing]
+    buf = api.get_symm_buffer_for_mega_moe(dist.group.WORLD, e, t_max, k, layer.hidden, layer.inter,
+                                           1 if layer.shared is not None else 0)
+    l1, l2, sl1, sl2 = H.kernel_weights(layer, dev, rank * e_l, (rank + 1) * e_l)
+    stats = torch.zeros(e_l, dtype=torch.int32, device=dev)
+    m = tokens_per_rank[rank]
+    y = torch.empty((m, layer.hidden), dtype=torch.bfloat16, device=dev)
+    for _ in range(2):                                                           # second call: cumulative statistics
+        api.stage_inputs_for_mega_moe(buf, hid[rank].to(dev), ids[rank].to(dev), w[rank].to(dev))
+        api.fp8_fp4_mega_moe(y, l1, l2, buf, sl1, sl2, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0)
+    read_status(buf)
+    bm = api.get_block_m_for_mega_moe(world, e, t_max, m, k)
+    plan = O.dispatch_plan(ids, e, rank, bm)
+    assert torch.equal(buf.recv_count.cpu().long(), plan.recv_count)
+    hdr, total, block_off = buf.plan_tables()
+    assert torch.equal(total.long(), plan.recv_total) and torch.equal(block_off.long(), plan.pool_block_offset)
+    assert torch.equal(stats.cpu().long(), 2 * plan.recv_total)
+    ref = O.moe_layer(hid, ids, w, layer.experts, layer.shared, 10.0, only_ranks=[rank])[rank]
+    met = O.parity_metrics(y.cpu(), ref)
+    assert met["rel_l2"] <= 1e-3, met
+    a, b = y.float().cpu(), ref.float()
+    ulp = torch.pow(2.0, torch.floor(torch.log2(b.abs().clamp(min=2.0 ** -126))) - 7)
+    assert float(((a - b).abs() - torch.clamp(ulp, min=2e-2)).max()) <= 0, met
