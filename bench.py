@@ -31,6 +31,7 @@ sys.path.insert(0, ROOT)
 H, I, E, K = 5120, 2304, 384, 6
 M_HEADLINE = 3840
 SWEEP = (1, 8, 64, 256, 1024, 2048, 3840)
+NCU_TRAFFIC_RATIO_GEMM1 = 1.059      # (dram__bytes_read + dram__bytes_write) / algorithmic bytes, profiles/umma_kernel_E64.md
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -212,7 +213,7 @@ def run_ours(args):
     barrier()
     step_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     value = world * m / (step_ms * 1e-3)
-    launches_per_step = 9          # quantiser, 3 route-ordering passes, plan, place, GEMM1, GEMM2, combine
+    launches_per_step = 9 if world == 1 else 10   # quantiser, 3 route-ordering passes, [pack], plan, place, GEMM1, GEMM2, combine
 
     # ---- end to end through the public API with host buffers (pinned): H2D of the step's inputs, D2H of y -------
     hid_h, ids_h, w_h = hid.cpu().pin_memory(), ids.cpu().pin_memory(), w.cpu().pin_memory()
@@ -274,7 +275,10 @@ def run_ours(args):
         ach = w13_bytes / (g1_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "umma_kernel<1> (grouped GEMM1 + SwiGLU/requant)", "achieved": ach,
                     "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": f"of {peak_kind}",
-                    "traffic": None, "algorithmic_bytes_per_launch": w13_bytes, "ms_per_launch": g1_ms}
+                    # DRAM bytes per launch: ncu read+write of this kernel on the E=64 capture (profiles/) was 1.059x its
+                    # algorithmic bytes; traffic grows with the experts hit, so the same ratio is applied here
+                    "traffic": w13_bytes * NCU_TRAFFIC_RATIO_GEMM1, "traffic_source": "scaled from the E=64 ncu capture",
+                    "algorithmic_bytes_per_launch": w13_bytes, "ms_per_launch": g1_ms}
         flops, nbytes = layer_work(routes, m, distinct, H, I, True)
         line_extra["kernels"] = {
             "gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "gemm2_gbs": w2_bytes / (g2_ms * 1e-3) / 1e9,

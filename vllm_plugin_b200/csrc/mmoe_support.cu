@@ -13,6 +13,55 @@ namespace mmoe {
 // clamped to [1, 254]; values multiplied by the exact reciprocal and rounded to nearest even.
 // One thread converts 8 elements (one 16-byte load, one 8-byte store); 4 threads share a scale, 16 a scale word.
 // =====================================================================================================================
+__device__ __forceinline__ void stage_vector(const uint4& raw, bool live, int64_t i, int vec_per_row, int h,
+                                             uint2* __restrict__ x_q, int32_t* __restrict__ x_sf,
+                                             int32_t* __restrict__ shared_sf, int64_t shared_rows, int shared_bm) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float v[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(p[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+    amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, 1e-4f);
+  const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
+  int e = static_cast<int>((bits >> 23) & 0xFFu) + ((bits & 0x7FFFFFu) != 0u);
+  e = min(max(e, 1), 254);
+  const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);   // exact reciprocal of 2^(e-127), e in [1, 253]
+  const float inv_exact = e == 254 ? __fdiv_rn(1.0f, __uint_as_float(254u << 23)) : inv;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    lo |= static_cast<uint32_t>(float_to_e4m3(__fmul_rn(v[j], inv_exact))) << (8 * j);
+    hi |= static_cast<uint32_t>(float_to_e4m3(__fmul_rn(v[4 + j], inv_exact))) << (8 * j);
+  }
+  if (live) x_q[i] = make_uint2(lo, hi);
+  // scale word: lanes 0,4,8,12 of each 16-lane group hold the four exponents
+  const int lane = threadIdx.x & 31;
+  const int base = lane & 16;
+  uint32_t word = static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 0));
+  word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 4)) << 8;
+  word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 8)) << 16;
+  word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 12)) << 24;
+  if (live && (lane & 15) == 0) {
+    const int64_t t = i / vec_per_row;
+    const int w = static_cast<int>(i - t * vec_per_row) / 16;
+    x_sf[t * (h / kTileK) + w] = static_cast<int32_t>(word);
+    if (shared_bm > 0) {
+      // row of token t in the BLOCK_M-dependent shared-expert scale layout (backend/staging.py:85-95)
+      const int64_t mm = t % shared_bm;
+      const int64_t bm_al = (shared_bm + 127) / 128 * 128;
+      const int64_t row = (t / shared_bm) * bm_al + (mm / 128) * 128 + (mm % 32) * 4 + (mm % 128) / 32;
+      shared_sf[(int64_t)w * shared_rows + row] = static_cast<int32_t>(word);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) stage_kernel(
     const uint4* __restrict__ hidden, uint2* __restrict__ x_q, int32_t* __restrict__ x_sf,
     int32_t* __restrict__ shared_sf, int64_t shared_rows, int shared_bm,
@@ -22,54 +71,22 @@ __global__ void __launch_bounds__(256) stage_kernel(
   const int64_t total = (int64_t)m * vec_per_row;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total_padded = (total + 31) / 32 * 32;   // whole warps iterate together (shuffles below)
-  for (int64_t i = tid; i < total_padded; i += stride) {
-    const bool live = i < total;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = hidden[i];
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float v[8];
-    float amax = 0.f;
+  const int64_t total_padded = (total + 31) / 32 * 32;   // whole warps iterate together (shuffles inside)
+  // four independent 16-byte loads in flight per thread before any of them is consumed
+  for (int64_t i = tid; i < total_padded; i += 4 * stride) {
+    uint4 raw[4];
+    bool live[4], active[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(p[j]);
-      v[2 * j] = f.x;
-      v[2 * j + 1] = f.y;
-      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    for (int u = 0; u < 4; ++u) {
+      const int64_t iu = i + u * stride;
+      active[u] = iu < total_padded;           // warp-uniform: stride and total_padded are multiples of 32
+      live[u] = iu < total;
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (live[u]) raw[u] = hidden[iu];
     }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, 1e-4f);
-    const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
-    int e = static_cast<int>((bits >> 23) & 0xFFu) + ((bits & 0x7FFFFFu) != 0u);
-    e = min(max(e, 1), 254);
-    const float inv = __fdiv_rn(1.0f, __uint_as_float(static_cast<uint32_t>(e) << 23));
-    uint32_t lo = 0, hi = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      lo |= static_cast<uint32_t>(float_to_e4m3(__fmul_rn(v[j], inv))) << (8 * j);
-      hi |= static_cast<uint32_t>(float_to_e4m3(__fmul_rn(v[4 + j], inv))) << (8 * j);
-    }
-    if (live) x_q[i] = make_uint2(lo, hi);
-    // scale word: lanes 0,4,8,12 of each 16-lane group hold the four exponents
-    const int lane = threadIdx.x & 31;
-    const int base = lane & 16;
-    uint32_t word = static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 0));
-    word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 4)) << 8;
-    word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 8)) << 16;
-    word |= static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, base + 12)) << 24;
-    if (live && (lane & 15) == 0) {
-      const int64_t t = i / vec_per_row;
-      const int w = static_cast<int>(i % vec_per_row) / 16;
-      x_sf[t * (h / kTileK) + w] = static_cast<int32_t>(word);
-      if (shared_bm > 0) {
-        // row of token t in the BLOCK_M-dependent shared-expert scale layout (backend/staging.py:85-95)
-        const int64_t mm = t % shared_bm;
-        const int64_t bm_al = (shared_bm + 127) / 128 * 128;
-        const int64_t row = (t / shared_bm) * bm_al + (mm / 128) * 128 + (mm % 32) * 4 + (mm % 128) / 32;
-        shared_sf[(int64_t)w * shared_rows + row] = static_cast<int32_t>(word);
-      }
-    }
+    for (int u = 0; u < 4; ++u)
+      if (active[u]) stage_vector(raw[u], live[u], i + u * stride, vec_per_row, h, x_q, x_sf, shared_sf, shared_rows, shared_bm);
   }
   // routing repack (backend/staging.py:244-251)
   const int64_t routes = (int64_t)m * k;
@@ -87,7 +104,8 @@ cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int 
   if (m == 0) return cudaSuccess;
   const int h = c.geo.hidden;
   const int64_t total = (int64_t)m * h / 8;
-  int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  int blocks = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, 148 * 8));
+  if (blocks < 1) blocks = 1;
   stage_kernel<<<blocks, 256, 0, s>>>(
       static_cast<const uint4*>(hidden), c.at<uint2>(c.lay.x), c.at<int32_t>(c.lay.x_sf),
       c.at<int32_t>(c.lay.shared_x_sf), c.lay.shared_sf_rows, c.geo.num_shared_experts > 0 ? shared_bm : 0, ids, ids64, w,

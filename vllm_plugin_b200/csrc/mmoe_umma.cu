@@ -33,6 +33,7 @@ constexpr int kThreads = 224;   // producer, MMA 0, 4 epilogue warps, MMA 1
 constexpr int kSmemBudget = 227 * 1024 - 2048;   // dynamic shared memory we ask for at most (alignment slack excluded)
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitHintNs = 200000;   // upper bound of one hardware-suspended barrier wait (the loop around it re-arms)
+constexpr int kSpinProbes = 0;             // non-blocking probes before a wait may suspend (measured: spinning is slower)
 
 struct UmmaParams {
   CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 128 rows
@@ -71,6 +72,7 @@ struct UmmaParams {
   int prefetch_ahead;          // K stages of weights requested from DRAM into L2 ahead of the pipeline (0 = off)
   int ablate;                  // timing experiments only (results become meaningless): bit 0 skip weight-scale copies,
                                // 1 token-scale copies, 2 token tiles, 3 tcgen05.cp, 4 MMAs, 5 weight tiles
+  CUtensorMap map_w_routed_packed;     // experiment only (ablate bit 7): the packed FP4 bytes as plain bytes
   CUtensorMap map_tok_routed_box[4];   // token maps with boxes of 16 / 32 / 64 / 128 rows
   CUtensorMap map_tok_shared_box[4];
 };
@@ -103,6 +105,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity), "r"(kWaitHintNs)     // the thread sleeps in hardware until the phase completes or the hint expires
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -233,9 +247,14 @@ struct Waiter {
   }
   // true when the phase completed, false when the call is being abandoned
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
+    // short non-blocking spin first: a hardware-suspended wait wakes up late, and that latency lands on the critical
+    // path of whichever role the pipeline is waiting for
+#pragma unroll 1
+    for (int i = 0; i < kSpinProbes; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
     for (uint32_t spin = 0;; ++spin) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((spin & 3u) == 3u) {
+      if ((spin & 63u) == 63u) {
         if (ctl->abort_flag != 0) return false;
         if (global_timer() > deadline) {
           ctl->abort_flag = 1;
@@ -339,7 +358,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int n16 = (tile.n_valid + 15) & ~15;
         int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : 3));
         if ((16 << box_sel) > kBoxRows) box_sel = kBoxRows == 16 ? 0 : (kBoxRows == 32 ? 1 : (kBoxRows == 64 ? 2 : 3));
-        const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
+        const CUtensorMap* wmap = shared ? &p.map_w_shared : ((ab & 128) ? &p.map_w_routed_packed : &p.map_w_routed);
+        const int kdiv = (!shared && (ab & 128)) ? 2 : 1;      // byte coordinates of the packed view
         const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
         const int e = shared ? 0 : tile.expert;
         // The 256 stored weight rows of the task.  Layer 1 reads W13 in its stored order [g0..7, u0..7, g8..15, ...]
@@ -370,8 +390,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
           const uint32_t a_dst = a0 + stage * S::kABytes;
           const uint32_t sf_dst = sf0 + stage * S::kSfBytes;
           if (!(ab & 32)) {
-            if (kLayer == 1) tma_load_5d(a_dst, wmap, k0, 0, group, 0, slice, bar);
-            else tma_load_3d(a_dst, wmap, k0, row, slice, bar);
+            if (kLayer == 1) tma_load_5d(a_dst, wmap, k0 / kdiv, 0, group, 0, slice, bar);
+            else tma_load_3d(a_dst, wmap, k0 / kdiv, row, slice, bar);
             // ask DRAM for a later K stage of this task now: it needs no shared memory, only L2
             if (p.prefetch_ahead > 0 && kb + p.prefetch_ahead < k_stages) {
               if (kLayer == 1) tma_prefetch_5d(wmap, k0 + p.prefetch_ahead * kTileK, 0, group, 0, slice);
@@ -650,6 +670,33 @@ int make_w13_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems,
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// experiment only: the packed FP4 bytes of a weight tensor as a plain byte tensor (no expansion), same box geometry
+int make_packed_map(CUtensorMap* map, bool w13, const void* base, uint64_t k_elems, uint64_t rows_total, int64_t slice_stride) {
+  const uint64_t row_bytes = k_elems / 2;
+  const uint64_t slices = slice_stride > 0 ? 2 : 1;
+  const uint64_t rows = rows_total / slices;
+  const uint64_t sl = slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes;
+  CUresult r;
+  if (w13) {
+    const cuuint64_t dims[5] = {row_bytes, 8, rows / 16, 2, slices};
+    const cuuint64_t strides[4] = {row_bytes, 16 * row_bytes, 8 * row_bytes, sl};
+    const cuuint32_t box[5] = {kTileK / 2, 8, 16, 2, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void*>(base), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[3] = {row_bytes, rows, slices};
+    const cuuint64_t strides[2] = {row_bytes, sl};
+    const cuuint32_t box[3] = {kTileK / 2, 2 * kTileRows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 template <int kLayer, int kBoxRows>
 cudaError_t prepare_one() {
   return cudaFuncSetAttribute(umma_kernel<kLayer, kBoxRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -731,6 +778,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
     p1.map_w_shared = p1.map_w_routed;
     p1.map_tok_shared = p1.map_tok_routed;
   }
+  bad |= make_packed_map(&p1.map_w_routed_packed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
   for (int b = 0; b < 4; ++b) {
     bad |= make_map(&p1.map_tok_routed_box[b], false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, 16u << b, false);
     if (has_shared) bad |= make_map(&p1.map_tok_shared_box[b], false, c.ws + c.lay.x, h, c.geo.num_max_tokens, 16u << b, false);
@@ -775,6 +823,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
     p2.map_w_shared = p2.map_w_routed;
     p2.map_tok_shared = p2.map_tok_routed;
   }
+  bad |= make_packed_map(&p2.map_w_routed_packed, false, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
   for (int b = 0; b < 4; ++b) {
     bad |= make_map(&p2.map_tok_routed_box[b], false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, 16u << b, false);
     if (has_shared) bad |= make_map(&p2.map_tok_shared_box[b], false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, 16u << b, false);
