@@ -36,8 +36,19 @@ def test_small_layer_matches_oracle(engine, m, shared):
     layer = H.make_layer(shared=shared, seed=m, **SMALL)
     hid = O.make_hidden(m, layer.hidden, 1)
     ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 2, mask_frac=0.1 if m > 1 else 0.0)
-    y, _ = H.run_layer(layer, hid, ids, w, engine=engine)
+    y, buf = H.run_layer(layer, hid, ids, w, engine=engine)
     assert_parity(y, H.oracle_layer(layer, hid, ids, w), f"engine {engine} m {m}")
+    # the dispatch tables of the call (M <= 128 takes the fused single-launch route/plan kernel) against the oracle
+    hdr, total, block_off = buf.plan_tables()
+    plan = O.dispatch_plan([ids], layer.num_experts, 0, hdr["block_m"])
+    assert torch.equal(buf.send_count.cpu().long(), plan.recv_total) and torch.equal(total.long(), plan.recv_total)
+    assert torch.equal(block_off.long(), plan.pool_block_offset)
+    pos = buf.route_pos[:m].cpu()
+    dst = buf.pool_dst.cpu()
+    inv = {int(pos[t, s]): (t, s) for t in range(m) for s in range(layer.num_topk) if int(pos[t, s]) >= 0}
+    for ex in range(layer.num_experts):
+        base = int(block_off[ex]) * hdr["block_m"]
+        assert [inv[int(dst[base + j])] for j in range(int(total[ex]))] == [(t, s) for (_, t, s) in plan.routes[ex]]
 
 
 @pytest.mark.parametrize("bm", [16, 32, 64, 128, 192, 240])

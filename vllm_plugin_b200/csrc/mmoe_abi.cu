@@ -352,8 +352,19 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
                  void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream) {
   if (geo != nullptr && geo->num_ranks != 1)
     return fail(MMOE_ERR_INVALID_ARGUMENT, "mmoe_forward is the single-rank sequence; call the steps for num_ranks > 1");
-  int rc = mmoe_dispatch_count(geo, workspace, num_tokens, stream);
-  if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
+  int rc;
+  if (geo != nullptr && num_tokens > 0 && num_tokens <= 128 && geo->num_experts <= 512 && valid_block_m(block_m) && workspace != nullptr) {
+    // decode: one launch orders the routes and builds the plan
+    mmoe::Ctx c;
+    rc = make_ctx(geo, workspace, &c);
+    if (rc == MMOE_OK) {
+      cudaError_t e = mmoe::launch_route_plan_place_small(c, num_tokens, block_m, stats, static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) rc = cuda_fail(e, "route/plan launch");
+    }
+  } else {
+    rc = mmoe_dispatch_count(geo, workspace, num_tokens, stream);
+    if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
+  }
   if (rc == MMOE_OK) rc = mmoe_experts(geo, workspace, weights, opt, num_tokens, block_m, stream);
   if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
   return rc;

@@ -16,6 +16,10 @@ constexpr int kTileK = 128;        // K elements per pipeline stage = one packed
 constexpr int kTileRows = 128;     // weight rows per tile (UMMA M)
 constexpr int kChunkRows = 128;    // token rows per scale-factor chunk (one 512-byte tcgen05.cp source per K stage)
 constexpr int kMaxTileTokens = 112;  // largest UMMA N of one task; a fuller chunk is split into two 64-token halves
+// Largest token tile of a BLOCK_M variant.  BLOCK_M = 128 caps its tiles at 80 rows (fuller chunks are split in two):
+// the 10 KB token slot buys a fifth pipeline stage, and at the token counts that select BLOCK_M = 128 a block with
+// more than 80 rows is a 2.6-sigma event.  192 / 240 keep 112.
+__host__ __device__ inline int max_tile_rows(int block_m) { return block_m <= 64 ? block_m : (block_m == 128 ? 80 : kMaxTileTokens); }
 constexpr int kSortChunkTokens = 128;
 constexpr int kSharedExpert = -2;  // MmoeTile::expert of a shared-expert tile
 
@@ -166,6 +170,7 @@ cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int 
                          const uint8_t* pad, int m, int shared_bm, cudaStream_t s);
 cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s);
+cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
 cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
 cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s);
 cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);

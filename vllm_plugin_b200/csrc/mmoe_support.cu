@@ -295,9 +295,6 @@ cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s) {
 // (backend/kernel/dispatch.py:431-447); inside an expert, source ranks ascending and each source's routes in its send
 // order (token, slot) -- a fixed order where the reference's is arrival order.
 // =====================================================================================================================
-__device__ __forceinline__ int tiles_of_rows(int rows_in_chunk) {
-  return rows_in_chunk <= 0 ? 0 : (rows_in_chunk > kMaxTileTokens ? 2 : 1);
-}
 
 __device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int first_block, bool write) {
   // tokens [0, n) of one expert laid out in blocks of block_m rows starting at pool block `first_block`
@@ -310,7 +307,7 @@ __device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_
       if (rows <= 0) break;
       const int row0 = row_base + b * block_m + s * kChunkRows;
       const int chunk = (first_block + b) * chunks_per_block + s;
-      if (rows > kMaxTileTokens) {
+      if (rows > max_tile_rows(block_m)) {
         if (write) {
           out[count] = Tile{expert, row0, 64, chunk, 0, {0, 0, 0}};
           out[count + 1] = Tile{expert, row0 + 64, rows - 64, chunk, 2, {0, 0, 0}};
@@ -388,6 +385,94 @@ __global__ void __launch_bounds__(1024) plan_kernel(
   }
 }
 
+// Decode path at EP1 (one chunk of at most 128 tokens): route ordering and pool plan in ONE single-block launch
+// instead of four, because at a handful of tokens the layer is bound by launch latency.  Same results as
+// sort_local/scan/place + plan_kernel (tested against them).
+__global__ void __launch_bounds__(1024) route_plan_small_kernel(
+    const int64_t* __restrict__ topk_idx, int32_t* __restrict__ route_pos, int32_t* __restrict__ sorted_route,
+    int32_t* __restrict__ send_count, int32_t* __restrict__ send_offset, int32_t* __restrict__ recv_count,
+    char* __restrict__ plan_base, int32_t* __restrict__ stats, int32_t* __restrict__ status, int m, int k,
+    int num_experts, int block_m, int has_shared) {
+  extern __shared__ int32_t sm[];
+  int32_t* ids = sm;                              // [m*k]
+  int32_t* hist = sm + kSortChunkTokens * k;      // [E]
+  int32_t* off = hist + num_experts;              // [E+1]  send offsets
+  int32_t* boff = off + num_experts + 1;          // [E+1]  pool block offsets
+  int32_t* toff = boff + num_experts + 1;         // [E+1]  tile offsets
+  PlanView pv = plan_view(plan_base, num_experts, 1);
+  const int n = m * k;
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int64_t id = topk_idx[i];
+    if (id >= num_experts) { report_bad_index(status); id = -1; }
+    ids[i] = id < 0 ? -1 : static_cast<int32_t>(id);
+  }
+  __syncthreads();
+  int rank[4];                                    // n <= 128 * 31 < 4 * 1024
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = threadIdx.x + u * blockDim.x;
+    rank[u] = -1;
+    if (i < n && ids[i] >= 0) {
+      int r = 0;
+      for (int j = 0; j < i; ++j) r += (ids[j] == ids[i]);
+      rank[u] = r;
+      atomicAdd(&hist[ids[i]], 1);                // a count, not an order
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int so = 0, bo = 0, to = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      off[e] = so; boff[e] = bo; toff[e] = to;
+      const int tot = hist[e];
+      so += tot;
+      bo += (tot + block_m - 1) / block_m;
+      to += emit_tiles(nullptr, e, 0, tot, block_m, 0, false);
+    }
+    off[num_experts] = so; boff[num_experts] = bo; toff[num_experts] = to;
+    pv.hdr->num_routed_tiles = to;
+    pv.hdr->num_pool_blocks = bo;
+    pv.hdr->total_recv = so;
+    pv.hdr->block_m = block_m;
+    pv.hdr->num_tokens = m;
+    pv.hdr->num_shared_tiles = has_shared ? emit_tiles(pv.tiles + to, kSharedExpert, 0, m, block_m, 0, true) : 0;
+    pv.rank_off[0] = 0;
+    pv.rank_off[1] = so;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = threadIdx.x + u * blockDim.x;
+    if (i < n) {
+      int pos = -1;
+      if (rank[u] >= 0) {
+        pos = off[ids[i]] + rank[u];
+        sorted_route[pos] = i;
+      }
+      route_pos[i] = pos;
+    }
+  }
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    const int tot = hist[e];
+    send_count[e] = tot;
+    recv_count[e] = tot;
+    send_offset[e] = off[e];
+    pv.expert_total[e] = tot;
+    pv.expert_block_off[e] = boff[e];
+    pv.expert_tile_off[e] = toff[e];
+    pv.seg_pool_start[e] = boff[e] * block_m;
+    pv.seg_recv_start[e] = off[e];
+    if (stats != nullptr) stats[e] += tot;
+    emit_tiles(pv.tiles + toff[e], e, boff[e] * block_m, tot, block_m, boff[e], true);
+  }
+  if (threadIdx.x == 0) {
+    send_offset[num_experts] = off[num_experts];
+    pv.expert_block_off[num_experts] = boff[num_experts];
+    pv.expert_tile_off[num_experts] = toff[num_experts];
+  }
+}
+
 // Place: one warp per pool row of every routed tile: copy the FP8 row, scatter its scale words into the chunk layout,
 // record the top-k weight and the receive-order row that takes the expert output.
 __global__ void __launch_bounds__(256) place_kernel(
@@ -432,6 +517,22 @@ __global__ void __launch_bounds__(256) place_kernel(
       }
     }
   }
+}
+
+// EP1, M <= 128: fused route ordering + plan, then placement
+cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {
+  const int k = c.geo.num_topk, e = c.geo.num_experts;
+  const size_t smem = (size_t)(kSortChunkTokens * k + 4 * e + 3) * sizeof(int32_t);
+  route_plan_small_kernel<<<1, 1024, smem, s>>>(
+      c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos), c.at<int32_t>(c.lay.sorted_route),
+      c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.recv_count),
+      c.ws + c.lay.plan, stats, c.at<int32_t>(c.lay.status), m, k, e, block_m, c.geo.num_shared_experts > 0);
+  place_kernel<<<148 * 2, 256, 0, s>>>(
+      c.ws + c.lay.plan, c.at<uint4>(c.lay.x), c.at<int32_t>(c.lay.x_sf), c.at<float>(c.lay.topk_weights),
+      c.at<int32_t>(c.lay.sorted_route), c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf),
+      c.at<float>(c.lay.pool_w), c.at<int32_t>(c.lay.pool_dst), c.lay.pool_sf_rows, c.e_local, 1, c.geo.hidden,
+      c.geo.num_topk, 1);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {

@@ -73,8 +73,8 @@ struct UmmaParams {
   int ablate;                  // timing experiments only (results become meaningless): bit 0 skip weight-scale copies,
                                // 1 token-scale copies, 2 token tiles, 3 tcgen05.cp, 4 MMAs, 5 weight tiles
   CUtensorMap map_w_routed_packed;     // experiment only (ablate bit 7): the packed FP4 bytes as plain bytes
-  CUtensorMap map_tok_routed_box[4];   // token maps with boxes of 16 / 32 / 64 / 128 rows
-  CUtensorMap map_tok_shared_box[4];
+  CUtensorMap map_tok_routed_box[5];   // token maps with boxes of 16 / 32 / 64 / 80 / 128 rows
+  CUtensorMap map_tok_shared_box[5];
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -276,7 +276,7 @@ struct Waiter {
 // accumulator each.
 template <int kLayer, int kBoxRows>
 struct Shape {
-  static constexpr int kNCap = kBoxRows > kMaxTileTokens ? kMaxTileTokens : kBoxRows;   // accumulator columns per matrix
+  static constexpr int kNCap = kBoxRows > kMaxTileTokens ? kMaxTileTokens : kBoxRows;   // accumulator columns per matrix (kBoxRows = largest tile)
   static constexpr int kABytes = 2 * kTileRows * kTileK;           // byte containers in shared memory
   static constexpr int kBBytes = kBoxRows * kTileK;
   // scale area of a stage: [A scales in tensor-memory order: 2 x 512][token scales 512][layer 1: raw 1024]
@@ -356,8 +356,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const bool shared = tile.expert == kSharedExpert;
         // smallest token box that covers the tile (16 / 32 / 64 / 128 rows): fewer rows to move and to pad
         const int n16 = (tile.n_valid + 15) & ~15;
-        int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : 3));
-        if ((16 << box_sel) > kBoxRows) box_sel = kBoxRows == 16 ? 0 : (kBoxRows == 32 ? 1 : (kBoxRows == 64 ? 2 : 3));
+        const int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : (n16 <= 80 ? 3 : 4)));   // never above kBoxRows
+        const uint32_t box_rows = box_sel == 3 ? 80u : (box_sel == 4 ? 128u : (16u << box_sel));
         const CUtensorMap* wmap = shared ? &p.map_w_shared : ((ab & 128) ? &p.map_w_routed_packed : &p.map_w_routed);
         const int kdiv = (!shared && (ab & 128)) ? 2 : 1;      // byte coordinates of the packed view
         const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const uint32_t a_tx = shared ? 2 * kTileRows * kTileK : kTileRows * kTileK;   // packed FP4 counts its global bytes
         uint32_t tx = 0;
         if (!(ab & 32)) tx += a_tx;
-        if (!(ab & 4)) tx += (16u << box_sel) * kTileK;
+        if (!(ab & 4)) tx += box_rows * kTileK;
         if (!(ab & 1)) tx += 1024;
         if (!(ab & 2)) tx += 512;
         int k0 = 0;
@@ -714,7 +714,7 @@ cudaError_t launch_one(const UmmaParams& p0, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-int box_rows_of(int block_m) { return block_m <= 16 ? 16 : (block_m <= 32 ? 32 : (block_m <= 64 ? 64 : 128)); }
+int box_rows_of(int block_m) { return block_m <= 16 ? 16 : (block_m <= 32 ? 32 : (block_m <= 64 ? 64 : (block_m == 128 ? 80 : 128))); }
 
 template <int kLayer>
 cudaError_t launch_layer(const UmmaParams& p, int box, cudaStream_t s) {
@@ -722,6 +722,7 @@ cudaError_t launch_layer(const UmmaParams& p, int box, cudaStream_t s) {
     case 16: return launch_one<kLayer, 16>(p, s);
     case 32: return launch_one<kLayer, 32>(p, s);
     case 64: return launch_one<kLayer, 64>(p, s);
+    case 80: return launch_one<kLayer, 80>(p, s);
     default: return launch_one<kLayer, 128>(p, s);
   }
 }
@@ -751,10 +752,12 @@ int prepare_umma(const MmoeGeometry& geo) {
   if (e == cudaSuccess) e = prepare_one<1, 16>();
   if (e == cudaSuccess) e = prepare_one<1, 32>();
   if (e == cudaSuccess) e = prepare_one<1, 64>();
+  if (e == cudaSuccess) e = prepare_one<1, 80>();
   if (e == cudaSuccess) e = prepare_one<1, 128>();
   if (e == cudaSuccess) e = prepare_one<2, 16>();
   if (e == cudaSuccess) e = prepare_one<2, 32>();
   if (e == cudaSuccess) e = prepare_one<2, 64>();
+  if (e == cudaSuccess) e = prepare_one<2, 80>();
   if (e == cudaSuccess) e = prepare_one<2, 128>();
   return e == cudaSuccess ? MMOE_OK : MMOE_ERR_CUDA;
 }
@@ -779,9 +782,10 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
     p1.map_tok_shared = p1.map_tok_routed;
   }
   bad |= make_packed_map(&p1.map_w_routed_packed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
-  for (int b = 0; b < 4; ++b) {
-    bad |= make_map(&p1.map_tok_routed_box[b], false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, 16u << b, false);
-    if (has_shared) bad |= make_map(&p1.map_tok_shared_box[b], false, c.ws + c.lay.x, h, c.geo.num_max_tokens, 16u << b, false);
+  const uint32_t kBoxes[5] = {16, 32, 64, 80, 128};
+  for (int b = 0; b < 5; ++b) {
+    bad |= make_map(&p1.map_tok_routed_box[b], false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b], false);
+    if (has_shared) bad |= make_map(&p1.map_tok_shared_box[b], false, c.ws + c.lay.x, h, c.geo.num_max_tokens, kBoxes[b], false);
     else p1.map_tok_shared_box[b] = p1.map_tok_routed_box[b];
   }
   if (bad) return cudaErrorInvalidValue;
@@ -824,9 +828,9 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
     p2.map_tok_shared = p2.map_tok_routed;
   }
   bad |= make_packed_map(&p2.map_w_routed_packed, false, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
-  for (int b = 0; b < 4; ++b) {
-    bad |= make_map(&p2.map_tok_routed_box[b], false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, 16u << b, false);
-    if (has_shared) bad |= make_map(&p2.map_tok_shared_box[b], false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, 16u << b, false);
+  for (int b = 0; b < 5; ++b) {
+    bad |= make_map(&p2.map_tok_routed_box[b], false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b], false);
+    if (has_shared) bad |= make_map(&p2.map_tok_shared_box[b], false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, kBoxes[b], false);
     else p2.map_tok_shared_box[b] = p2.map_tok_routed_box[b];
   }
   if (bad) return cudaErrorInvalidValue;
