@@ -73,6 +73,7 @@ typedef struct MmoeLayout {
   int64_t ret;              /* bf16 [R*T*kmax, H]  expert outputs in receive order (EP1: == send order) */
   int64_t ret_recv;         /* EP>1 only: bf16 [T*kmax, H] outputs returned to this rank, in send order */
   int64_t shared_out;       /* bf16 [T, H] */
+  int64_t ep_sync;          /* EP>1 only: epoch, per-barrier arrival flags and the [R][R] route-total table of the peer exchange */
   int64_t status;           /* int32 [8] device status words, zero = healthy */
   int64_t pool_rows;        /* row capacity of pool_x / act_x */
   int64_t pool_sf_rows;     /* row capacity (multiple of 128) of the pool SF chunk matrices */
@@ -155,6 +156,18 @@ int mmoe_route_order_noalloc(const int64_t* topk_idx, int32_t num_tokens, int32_
 
 /* EP>1: gather rows, scales and weights into send order. */
 int mmoe_dispatch_pack(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream);
+/* EP>1, device-side transport: the all-to-all of counts and rows as peer-memory stores over NVLink instead of host-issued
+ * collectives.  `peer_workspaces[r]` is rank r's workspace mapped into this process (symmetric allocation; entry
+ * [rank] is this rank's own).  `mmoe_ep_dispatch` runs after `mmoe_dispatch_count` and leaves `recv_count` and the
+ * receive buffers filled exactly as the host-driven exchange would; `mmoe_ep_return` runs after `mmoe_experts` and
+ * fills `ret_recv`.  Every rank of the group must make the same calls in the same order.  Replaces the in-kernel NVLink
+ * dispatch / write-back / barriers of the reference (backend/kernel/dispatch.py:348-589, epilogue.py:407-413,
+ * comm.py:277-318). */
+int mmoe_ep_dispatch(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces, int32_t num_tokens,
+                     const MmoeOptions* opt, void* stream);
+int mmoe_ep_return(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces, const MmoeOptions* opt,
+                   void* stream);
+
 /* Build the pool plan from `recv_count`, place received rows into the BLOCK_M-aligned pool, add the per-expert totals
  * to `stats` (int32 [E/R], may be NULL).  `total_recv_rows` bounds the rows present in receive order. */
 int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, int32_t block_m,

@@ -119,7 +119,7 @@ def exchange_body(rank, world, num_experts, k, tokens_per_rank, seed):
     assert torch.equal(back[: len(routes)], send_rows)
 
 
-def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max):
+def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, transport="peer", graph=False):
     """Whole layer at EP = world on GPUs: per-rank output against the oracle, receive counts and statistics bit-exact."""
     import helpers as H
     from oracle import mmoe_oracle as O
@@ -140,9 +140,29 @@ def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max):
     stats = torch.zeros(e_l, dtype=torch.int32, device=dev)
     m = tokens_per_rank[rank]
     y = torch.empty((m, layer.hidden), dtype=torch.bfloat16, device=dev)
-    for _ in range(2):                                                           # second call: cumulative statistics
-        api.stage_inputs_for_mega_moe(buf, hid[rank].to(dev), ids[rank].to(dev), w[rank].to(dev))
+    api.set_kernel_options(ep_transport=transport)
+    if transport == "peer":
+        assert buf.peer_ptrs is not None, "symmetric memory was expected to be available"
+    hid_d, ids_d, w_d = hid[rank].to(dev), ids[rank].to(dev), w[rank].to(dev)
+
+    def call():
+        api.stage_inputs_for_mega_moe(buf, hid_d, ids_d, w_d)
         api.fp8_fp4_mega_moe(y, l1, l2, buf, sl1, sl2, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0)
+
+    call()
+    if graph:                                                                    # second call as a CUDA-graph replay
+        api.precompile_mega_moe_variants(world, e, t_max, k, layer.hidden, layer.inter, 1 if layer.shared is not None else 0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        snapshot = stats.clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call()
+        stats.copy_(snapshot)          # the capture itself does not run the kernels; keep "one call so far"
+        y.zero_()
+        g.replay()
+    else:
+        call()                                                                   # second call: cumulative statistics
     read_status(buf)
     bm = api.get_block_m_for_mega_moe(world, e, t_max, m, k)
     plan = O.dispatch_plan(ids, e, rank, bm)

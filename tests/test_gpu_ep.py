@@ -17,11 +17,15 @@ def _need(n):
 SMALL = dict(hidden=512, inter=256, num_experts=16, num_topk=4, shared=True)
 
 
-@pytest.mark.parametrize("world,tokens,kw", [
-    (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2)),
-    (2, (1, 0), {}),
-    (4, (130, 64, 7, 300), dict(zipf_s=1.2, mask_frac=0.05)),
+@pytest.mark.parametrize("world,tokens,kw,transport,graph", [
+    (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "peer", False),
+    (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "nccl", False),
+    (2, (1, 0), {}, "peer", False),
+    (2, (40, 130), dict(zipf_s=1.2, mask_frac=0.05), "peer", True),
+    (4, (130, 64, 7, 300), dict(zipf_s=1.2, mask_frac=0.05), "peer", False),
 ])
-def test_layer_matches_oracle_at_ep(world, tokens, kw):
+def test_layer_matches_oracle_at_ep(world, tokens, kw, transport, graph):
+    """Per-rank output against the oracle, receive counts / block offsets / statistics bit-exact; with the device-side
+    peer exchange (also replayed from a CUDA graph) and with the host-driven NCCL exchange."""
     _need(world)
-    run_ranks(world, "nccl", layer_body, SMALL, tokens, 3, kw, 1920, timeout=600)
+    run_ranks(world, "nccl", layer_body, SMALL, tokens, 3, kw, 1920, transport, graph, timeout=240)

@@ -28,7 +28,7 @@ ENGINE_SCALAR_VALIDATION = 1
 EXPORTED_SYMBOLS = (
     "mmoe_layout", "mmoe_block_m", "mmoe_prepare", "mmoe_stage_inputs", "mmoe_dispatch_count", "mmoe_dispatch_pack",
     "mmoe_dispatch_place", "mmoe_experts", "mmoe_combine", "mmoe_forward", "mmoe_read_status", "mmoe_status_string",
-    "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc",
+    "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc", "mmoe_ep_dispatch", "mmoe_ep_return",
 )
 
 
@@ -42,7 +42,7 @@ _LAYOUT_FIELDS = (
     "total_bytes", "x", "x_sf", "topk_idx", "topk_weights", "shared_x_sf", "shared_sf_rows", "send_count",
     "send_offset", "route_pos", "sorted_route", "sort_scratch", "recv_count", "plan", "send_x", "send_sf", "send_w",
     "recv_x", "recv_sf", "recv_w", "pool_x", "pool_sf", "pool_w", "pool_dst", "act_x", "act_sf", "shared_act_x",
-    "shared_act_sf", "ret", "ret_recv", "shared_out", "status", "pool_rows", "pool_sf_rows", "max_routes", "max_tiles")
+    "shared_act_sf", "ret", "ret_recv", "shared_out", "ep_sync", "status", "pool_rows", "pool_sf_rows", "max_routes", "max_tiles")
 
 
 class MmoeLayout(ctypes.Structure):
@@ -96,6 +96,8 @@ def load() -> ctypes.CDLL:
     lib.mmoe_last_error.restype = ctypes.c_char_p
     lib.mmoe_abi_version.argtypes = []
     lib.mmoe_set_tuning.argtypes = [i32, i32]
+    lib.mmoe_ep_dispatch.argtypes = [geo_p, vp, ctypes.POINTER(vp), i32, ctypes.POINTER(MmoeOptions), vp]
+    lib.mmoe_ep_return.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeOptions), vp]
     lib.mmoe_route_order_noalloc.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
     for name in EXPORTED_SYMBOLS:
         fn = getattr(lib, name)

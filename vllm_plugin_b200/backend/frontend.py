@@ -29,6 +29,8 @@ class KernelOptions:
     block_m: int = 0          # > 0 forces the BLOCK_M variant
     timeout_ms: int = 2000    # bound of every device-side wait
     engine: int = _native.ENGINE_TENSOR_CORE   # ENGINE_SCALAR_VALIDATION selects the scalar validation kernels (tests)
+    ep_transport: str = "peer"  # EP > 1: "peer" = device-side exchange over NVLink peer memory (graph-capturable),
+                                # "nccl" = host-driven all-to-allv (also used when symmetric memory is unavailable)
 
 
 _kernel_options = KernelOptions()
@@ -229,6 +231,15 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
         return
     group = sym_buffer.group
     _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
+    if sym_buffer.peer_ptrs is not None and _kernel_options.ep_transport == "peer":
+        # device-side exchange: no host round trip, capturable in a CUDA graph
+        peers = (ctypes.c_void_p * sym_buffer.num_ranks)(*sym_buffer.peer_ptrs)
+        _native.check(lib.mmoe_ep_dispatch(g, ws, peers, m, ctypes.byref(opts), stream))
+        _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
+        _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
+        _native.check(lib.mmoe_ep_return(g, ws, peers, ctypes.byref(opts), stream))
+        _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
+        return
     _native.check(lib.mmoe_dispatch_pack(g, ws, m, stream))
     send_splits, recv_splits = exchange_counts(group, sym_buffer.send_count, sym_buffer.recv_count)
     exchange_rows(group, sym_buffer.recv_x, sym_buffer.send_x, recv_splits, send_splits)

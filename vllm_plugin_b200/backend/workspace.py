@@ -45,9 +45,26 @@ class SymmBuffer:
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = device
-        self.buffer = torch.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
+        self.peer_ptrs = None          # EP > 1: every rank's buffer mapped into this process (symmetric allocation)
+        self.handle = None
+        if group.size() > 1 and device.type == "cuda":
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+
+                self.buffer = symm_mem.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
+                self.handle = symm_mem.rendezvous(self.buffer, group)
+                self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+                assert self.peer_ptrs[group.rank()] == self.buffer.data_ptr()
+            except Exception as exc:  # noqa: BLE001 - no symmetric memory: the host-driven NCCL exchange still works
+                warnings.warn(f"symmetric memory is unavailable ({type(exc).__name__}: {exc}); using the NCCL exchange")
+                self.peer_ptrs = None
+                self.handle = None
+                self.buffer = torch.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
+        else:
+            self.buffer = torch.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
         assert self.buffer.data_ptr() % 1024 == 0
         self.buffer.zero_()
+        torch.cuda.synchronize(device)
         if group.size() > 1:
             work = group.barrier()
             if hasattr(work, "wait"):

@@ -189,6 +189,7 @@ int mmoe_layout(const MmoeGeometry* g, MmoeLayout* out) {
   out->ret = take(max_recv * H * 2);
   out->ret_recv = take(ep ? max_routes * H * 2 : 0);
   out->shared_out = take(shared ? T * H * 2 : 0);
+  out->ep_sync = take(ep ? mmoe::ep_sync_bytes() : 0);
   out->status = take(64);
   out->total_bytes = off;
   out->pool_rows = pool_rows;
@@ -285,6 +286,38 @@ int mmoe_dispatch_pack(const MmoeGeometry* geo, void* workspace, int32_t num_tok
   if (geo->num_ranks == 1) return MMOE_OK;
   cudaError_t e = mmoe::launch_pack(c, num_tokens, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_pack launch");
+}
+
+static int check_peers(const MmoeGeometry* geo, void* workspace, const void* const* peers) {
+  if (geo->num_ranks < 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "the peer exchange needs num_ranks > 1");
+  if (peers == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "peer_workspaces is NULL");
+  for (int r = 0; r < geo->num_ranks; ++r)
+    if (peers[r] == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "peer_workspaces[%d] is NULL", r);
+  if (peers[geo->rank] != workspace) return fail(MMOE_ERR_INVALID_ARGUMENT, "peer_workspaces[rank] must be this rank's workspace");
+  return MMOE_OK;
+}
+
+int mmoe_ep_dispatch(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces, int32_t num_tokens,
+                     const MmoeOptions* opt, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc == MMOE_OK) rc = check_tokens(geo, num_tokens);
+  if (rc == MMOE_OK) rc = check_peers(geo, workspace, peer_workspaces);
+  if (rc != MMOE_OK) return rc;
+  const int64_t timeout_ns = (opt != nullptr && opt->timeout_ms > 0 ? (int64_t)opt->timeout_ms : 2000) * 1000000ll;
+  cudaError_t e = mmoe::launch_ep_dispatch(c, peer_workspaces, num_tokens, timeout_ns, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "ep_dispatch launch");
+}
+
+int mmoe_ep_return(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces, const MmoeOptions* opt,
+                   void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc == MMOE_OK) rc = check_peers(geo, workspace, peer_workspaces);
+  if (rc != MMOE_OK) return rc;
+  const int64_t timeout_ns = (opt != nullptr && opt->timeout_ms > 0 ? (int64_t)opt->timeout_ms : 2000) * 1000000ll;
+  cudaError_t e = mmoe::launch_ep_return(c, peer_workspaces, timeout_ns, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "ep_return launch");
 }
 
 int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, int32_t block_m, int32_t* stats,

@@ -181,5 +181,8 @@ cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_ex
                                int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route, cudaStream_t s);
 int route_order_static_max_tokens();
 int route_order_static_max_experts();
+int ep_sync_bytes();
+cudaError_t launch_ep_dispatch(const Ctx& c, const void* const* peer_ws, int m, int64_t timeout_ns, cudaStream_t s);
+cudaError_t launch_ep_return(const Ctx& c, const void* const* peer_ws, int64_t timeout_ns, cudaStream_t s);
 
 }  // namespace mmoe
