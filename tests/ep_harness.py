@@ -119,7 +119,7 @@ def exchange_body(rank, world, num_experts, k, tokens_per_rank, seed):
     assert torch.equal(back[: len(routes)], send_rows)
 
 
-def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, transport="peer", graph=False):
+def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, transport="peer", graph=False, replicas=0):
     """Whole layer at EP = world on GPUs: per-rank output against the oracle, receive counts and statistics bit-exact."""
     import helpers as H
     from oracle import mmoe_oracle as O
@@ -129,11 +129,27 @@ def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, 
     dev = torch.device("cuda", rank)
     layer = H.make_layer(seed=seed, **geometry)
     e, k = layer.num_experts, layer.num_topk
+    if replicas:
+        # load-balancer placement: the last `replicas` physical experts are copies of the hottest logical experts; the
+        # router's logical ids are mapped to a physical replica by (token + slot) % copies, as the engine does before
+        # the layer is called
+        logical = e - replicas
+        for j in range(replicas):
+            layer.experts[logical + j] = layer.experts[j]
     e_l = e // world
     hid = [O.make_hidden(tokens_per_rank[r], layer.hidden, seed + 10 + r) for r in range(world)]
     routing = [O.make_routing(tokens_per_rank[r], e, k, seed + 20 + r, **routing_kw) for r in range(world)]
     ids = [r_[0] for r_ in routing]
     w = [r_[1] for r_ in routing]
+    if replicas:
+        logical = e - replicas
+        for r in range(world):
+            lid = ids[r] % logical
+            lid = torch.where(ids[r] < 0, ids[r], lid)
+            tok = torch.arange(lid.shape[0]).view(-1, 1)
+            slot = torch.arange(k).view(1, -1)
+            use_copy = (lid >= 0) & (lid < replicas) & (((tok + slot) % 2) == 1)
+            ids[r] = torch.where(use_copy, lid + logical, lid)
     buf = api.get_symm_buffer_for_mega_moe(dist.group.WORLD, e, t_max, k, layer.hidden, layer.inter,
                                            1 if layer.shared is not None else 0)
     l1, l2, sl1, sl2 = H.kernel_weights(layer, dev, rank * e_l, (rank + 1) * e_l)

@@ -17,6 +17,13 @@ def _need(n):
 SMALL = dict(hidden=512, inter=256, num_experts=16, num_topk=4, shared=True)
 
 
+def test_redundant_physical_experts_under_cuda_graph():
+    """Load-balancer geometry: 12 logical + 4 redundant physical experts over 2 ranks, decode-sized calls replayed from
+    a CUDA graph."""
+    _need(2)
+    run_ranks(2, "nccl", layer_body, SMALL, (16, 64), 5, dict(zipf_s=1.2), 1920, "peer", True, 4, timeout=240)
+
+
 @pytest.mark.parametrize("world,tokens,kw,transport,graph", [
     (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "peer", False),
     (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "nccl", False),

@@ -118,6 +118,69 @@ cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int 
 // chunks of 128 tokens.  Replaces the atomics-ordered slot assignment of the reference (backend/kernel/dispatch.py:
 // 348-410) with a deterministic order; the per-expert counts are the same numbers.
 // =====================================================================================================================
+// ---------------------------------------------------------------------------------------------------------------------
+// small block-level building blocks of the route ordering and the plan
+// ---------------------------------------------------------------------------------------------------------------------
+// Exclusive prefix sum of `in[0..n)` into `out[0..n]` (out[n] = total), n <= 1024, whole block (>= 32 threads, a
+// multiple of 32) participates; `in` and `out` may not alias.  Ends with a barrier.
+__device__ void block_exclusive_scan(const int32_t* in, int32_t* out, int n) {
+  __shared__ int32_t warp_tot[33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __syncthreads();
+  int carry = 0;
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    int v = i < n ? in[i] : 0;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = lane < nwarps ? warp_tot[lane] : 0;
+      int wi = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, wi, d);
+        if (lane >= d) wi += t;
+      }
+      warp_tot[lane] = wi - w;                 // exclusive offset of each warp
+      if (lane == 31) warp_tot[32] = wi;       // block total of this round
+    }
+    __syncthreads();
+    if (i < n) out[i] = carry + warp_tot[warp] + incl - v;
+    carry += warp_tot[32];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[n] = carry;
+  __syncthreads();
+}
+
+// Stable rank of every route among the routes of the same expert, by ONE warp walking the routes in order, 32 at a
+// time: lanes with the same expert find each other with match.any, the lowest such lane owns the running counter.
+// `ids[i]` (-1 = masked) in shared memory, `count[e]` zeroed shared counters; writes rank[i] (or -1).
+__device__ void warp_rank_routes(const int32_t* ids, int n, int32_t* count, int32_t* rank) {
+  const int lane = threadIdx.x & 31;
+  for (int base = 0; base < n; base += 32) {
+    const int i = base + lane;
+    const int e = i < n ? ids[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    int r = -1;
+    if (e >= 0) {
+      const int before = __popc(peers & ((1u << lane) - 1u));
+      const int start = count[e];
+      r = start + before;
+    }
+    __syncwarp();
+    if (e >= 0 && (peers & ((1u << lane) - 1u)) == 0u) count[e] += __popc(peers);   // lowest lane of each expert group
+    __syncwarp();
+    if (i < n) rank[i] = r;
+  }
+}
+
 constexpr int kSortThreads = 256;
 constexpr int kMaxChunkRoutes = kSortChunkTokens * 32;
 
@@ -126,8 +189,8 @@ __global__ void __launch_bounds__(kSortThreads) sort_local_kernel(
     const int64_t* __restrict__ topk_idx, int32_t* __restrict__ route_pos, int32_t* __restrict__ chunk_count,
     int32_t* __restrict__ status, int m, int k, int num_experts) {
   extern __shared__ int32_t sm[];
-  int32_t* ids = sm;                       // [chunk routes]
-  int32_t* hist = sm + kSortChunkTokens * k;   // [num_experts]
+  int32_t* ids = sm;                                // [chunk routes]
+  int32_t* hist = sm + kSortChunkTokens * k;        // [num_experts]
   const int chunk = blockIdx.x;
   const int r0 = chunk * kSortChunkTokens * k;
   const int n = min(kSortChunkTokens * k, m * k - r0);
@@ -138,16 +201,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_local_kernel(
     ids[i] = id < 0 ? -1 : static_cast<int32_t>(id);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = ids[i];
-    int rank = -1;
-    if (e >= 0) {
-      rank = 0;
-      for (int j = 0; j < i; ++j) rank += (ids[j] == e);
-      atomicAdd(&hist[e], 1);             // a count, not an order: deterministic
-    }
-    route_pos[r0 + i] = rank;
-  }
+  if (threadIdx.x < 32) warp_rank_routes(ids, n, hist, route_pos + r0);
   __syncthreads();
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) chunk_count[(int64_t)chunk * num_experts + e] = hist[e];
 }
@@ -168,15 +222,9 @@ __global__ void __launch_bounds__(1024) sort_scan_kernel(
     send_count[e] = run;
     if (recv_count_if_single != nullptr) recv_count_if_single[e] = run;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < num_experts; ++e) {
-      send_offset[e] = run;
-      run += totals[e];
-    }
-    send_offset[num_experts] = run;
-  }
+  __shared__ int32_t offs[2048 + 1];
+  block_exclusive_scan(totals, offs, num_experts);
+  for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) send_offset[e] = offs[e];
 }
 
 // pass C: final position of every route, and the inverse map
@@ -344,19 +392,17 @@ __global__ void __launch_bounds__(1024) plan_kernel(
     s_tiles[e] = emit_tiles(nullptr, e, 0, tot, block_m, 0, false);
     if (stats != nullptr) stats[e] += tot;      // cumulative per-expert receive statistics (dispatch.py:644-650)
   }
-  __syncthreads();
+  __shared__ int32_t s_boff[514], s_toff[514];
+  block_exclusive_scan(s_blocks, s_boff, e_local);
+  block_exclusive_scan(s_tiles, s_toff, e_local);
+  for (int e = threadIdx.x; e <= e_local; e += blockDim.x) {
+    pv.expert_block_off[e] = s_boff[e];
+    pv.expert_tile_off[e] = s_toff[e];
+  }
   if (threadIdx.x == 0) {
-    int rb = 0, rt = 0;
-    for (int e = 0; e < e_local; ++e) {
-      pv.expert_block_off[e] = rb;
-      pv.expert_tile_off[e] = rt;
-      rb += s_blocks[e];
-      rt += s_tiles[e];
-    }
-    pv.expert_block_off[e_local] = rb;
-    pv.expert_tile_off[e_local] = rt;
+    const int rt = s_toff[e_local];
     pv.hdr->num_routed_tiles = rt;
-    pv.hdr->num_pool_blocks = rb;
+    pv.hdr->num_pool_blocks = s_boff[e_local];
     pv.hdr->block_m = block_m;
     pv.hdr->num_tokens = m;
     // shared-expert tiles: the call's own tokens in blocks of block_m (chunk numbering of backend/staging.py:85-95)
@@ -408,37 +454,29 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     ids[i] = id < 0 ? -1 : static_cast<int32_t>(id);
   }
   __syncthreads();
-  int rank[4];                                    // n <= 128 * 31 < 4 * 1024
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const int i = threadIdx.x + u * blockDim.x;
-    rank[u] = -1;
-    if (i < n && ids[i] >= 0) {
-      int r = 0;
-      for (int j = 0; j < i; ++j) r += (ids[j] == ids[i]);
-      rank[u] = r;
-      atomicAdd(&hist[ids[i]], 1);                // a count, not an order
-    }
-  }
+  int32_t* rank = toff + num_experts + 1;         // [m*k]
+  if (threadIdx.x < 32) warp_rank_routes(ids, n, hist, rank);
   __syncthreads();
+  int32_t* blocks = rank + kSortChunkTokens * k;  // [E] scratch of the scans
+  int32_t* tiles_n = blocks + num_experts;        // [E]
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    const int tot = hist[e];
+    blocks[e] = (tot + block_m - 1) / block_m;
+    tiles_n[e] = emit_tiles(nullptr, e, 0, tot, block_m, 0, false);
+  }
+  block_exclusive_scan(hist, off, num_experts);
+  block_exclusive_scan(blocks, boff, num_experts);
+  block_exclusive_scan(tiles_n, toff, num_experts);
   if (threadIdx.x == 0) {
-    int so = 0, bo = 0, to = 0;
-    for (int e = 0; e < num_experts; ++e) {
-      off[e] = so; boff[e] = bo; toff[e] = to;
-      const int tot = hist[e];
-      so += tot;
-      bo += (tot + block_m - 1) / block_m;
-      to += emit_tiles(nullptr, e, 0, tot, block_m, 0, false);
-    }
-    off[num_experts] = so; boff[num_experts] = bo; toff[num_experts] = to;
+    const int to = toff[num_experts];
     pv.hdr->num_routed_tiles = to;
-    pv.hdr->num_pool_blocks = bo;
-    pv.hdr->total_recv = so;
+    pv.hdr->num_pool_blocks = boff[num_experts];
+    pv.hdr->total_recv = off[num_experts];
     pv.hdr->block_m = block_m;
     pv.hdr->num_tokens = m;
     pv.hdr->num_shared_tiles = has_shared ? emit_tiles(pv.tiles + to, kSharedExpert, 0, m, block_m, 0, true) : 0;
     pv.rank_off[0] = 0;
-    pv.rank_off[1] = so;
+    pv.rank_off[1] = off[num_experts];
   }
   __syncthreads();
 #pragma unroll
@@ -446,8 +484,8 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     const int i = threadIdx.x + u * blockDim.x;
     if (i < n) {
       int pos = -1;
-      if (rank[u] >= 0) {
-        pos = off[ids[i]] + rank[u];
+      if (rank[i] >= 0) {
+        pos = off[ids[i]] + rank[i];
         sorted_route[pos] = i;
       }
       route_pos[i] = pos;
@@ -522,7 +560,7 @@ __global__ void __launch_bounds__(256) place_kernel(
 // EP1, M <= 128: fused route ordering + plan, then placement
 cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {
   const int k = c.geo.num_topk, e = c.geo.num_experts;
-  const size_t smem = (size_t)(kSortChunkTokens * k + 4 * e + 3) * sizeof(int32_t);
+  const size_t smem = (size_t)(2 * kSortChunkTokens * k + 6 * e + 3) * sizeof(int32_t);
   route_plan_small_kernel<<<1, 1024, smem, s>>>(
       c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos), c.at<int32_t>(c.lay.sorted_route),
       c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.recv_count),
