@@ -170,6 +170,8 @@ def run_ours(args):
     syn = SyntheticLayer(H, I, e_local, True, dev, seed=0, first_expert=rank * e_local)
     buf = api.get_symm_buffer_for_mega_moe(group, E, t_cap, K, H, I, 1)
     api.precompile_mega_moe_variants(world, E, t_cap, K, H, I, 1, activation_clamp=10.0)
+    api.set_kernel_options(ep_transport="nccl" if args.ep_transport == "nccl" else "peer",
+                           fuse_return=args.ep_transport == "peer")
     lib = _native.load()
     stats = torch.zeros(e_local, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev)
@@ -213,8 +215,9 @@ def run_ours(args):
     barrier()
     step_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     value = world * m / (step_ms * 1e-3)
-    # quantiser, 3 route-ordering passes, plan, place, GEMM1, GEMM2, combine; EP adds publish, push, return and 2 flag waits
-    launches_per_step = 9 if world == 1 else 14
+    # quantiser, 3 route-ordering passes, plan, place, GEMM1, GEMM2, combine; the peer exchange adds publish, push, the
+    # return copy (or, fused into GEMM2, its flag kernel) and 2 flag waits; the NCCL exchange adds the pack kernel
+    launches_per_step = 9 if world == 1 else (10 if args.ep_transport == "nccl" else 14)
 
     # ---- end to end through the public API with host buffers (pinned): every step copies its inputs host -> device and
     # its result device -> host inside the timed region.  The copies of step i+1 / i-1 run on a second stream while step
@@ -361,7 +364,7 @@ def run_ours(args):
             "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "mxfp8 x mxfp4 (e4m3 x e2m1, ue8m0 scales per 32), fp32 accumulate, bf16 out", "data": "synthetic",
             "config": {"workload": f"MegaMoE layer H={H} I={I} E={E} top-{K} 1 shared expert, EP{world}, M={m}/rank",
-                       "parallelism": f"ep{world}", "l2": "inputs larger than L2 (each step streams the packed weights of every expert hit)"},
+                       "parallelism": f"ep{world}", "ep_transport": args.ep_transport if world > 1 else None, "l2": "inputs larger than L2 (each step streams the packed weights of every expert hit)"},
             "e2e": {"value": world * m / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": e2e_ms},
             "gpu_launches": launches_per_step * args.steps,
@@ -397,6 +400,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--experts", type=int, default=E, help="physical experts (smaller values give a small profiling case)")
     ap.add_argument("--tokens", type=int, default=M_HEADLINE, help="tokens per rank of the timed step")
+    ap.add_argument("--ep-transport", default="peer", choices=("peer", "peer-unfused", "nccl"),
+                    help="N > 1: device-side NVLink exchange with the write-back fused into GEMM2 (default), the same "
+                         "with a separate copy kernel, or the host-driven NCCL all-to-allv")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

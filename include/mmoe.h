@@ -175,6 +175,14 @@ int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_to
 /* Grouped GEMM1 -> SwiGLU/requant -> grouped GEMM2 for routed and shared experts. */
 int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  int32_t num_tokens, int32_t block_m, void* stream);
+/* EP>1, device-side transport: `mmoe_experts` with the write-back fused into GEMM2 -- the epilogue stores every BF16
+ * output row straight into the `ret_recv` of the rank its token came from (peer stores over NVLink while the tensor
+ * cores work on the next tile), then barrier 2 is published and awaited.  Replaces `mmoe_experts` + `mmoe_ep_return`;
+ * the result in `ret_recv` is bit-identical.  This is the reference's in-kernel NVLink write-back
+ * (backend/kernel/epilogue.py:407-413, comm.py:277-318). */
+int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces,
+                           const MmoeWeights* weights, const MmoeOptions* opt, int32_t num_tokens, int32_t block_m,
+                           void* stream);
 /* y[t] = bf16(sum of the token's valid slots in ascending order, shared expert last). */
 int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream);
 /* EP1 convenience: count, place, experts, combine. */

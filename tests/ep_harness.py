@@ -156,7 +156,10 @@ def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, 
     stats = torch.zeros(e_l, dtype=torch.int32, device=dev)
     m = tokens_per_rank[rank]
     y = torch.empty((m, layer.hidden), dtype=torch.bfloat16, device=dev)
-    api.set_kernel_options(ep_transport=transport)
+    fused = transport != "peer-unfused"
+    if transport == "peer-unfused":
+        transport = "peer"
+    api.set_kernel_options(ep_transport=transport, fuse_return=fused)
     if transport == "peer":
         assert buf.peer_ptrs is not None, "symmetric memory was expected to be available"
     hid_d, ids_d, w_d = hid[rank].to(dev), ids[rank].to(dev), w[rank].to(dev)
@@ -180,6 +183,16 @@ def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, 
     else:
         call()                                                                   # second call: cumulative statistics
     read_status(buf)
+    if transport == "peer" and fused and not graph:
+        # the write-back fused into GEMM2 and the separate copy kernel must leave identical rows
+        y_fused = y.clone()
+        snapshot = stats.clone()
+        api.set_kernel_options(fuse_return=False)
+        call()
+        api.set_kernel_options(fuse_return=True)
+        read_status(buf)
+        stats.copy_(snapshot)
+        assert torch.equal(y, y_fused), "fused and unfused write-back differ"
     bm = api.get_block_m_for_mega_moe(world, e, t_max, m, k)
     plan = O.dispatch_plan(ids, e, rank, bm)
     assert torch.equal(buf.recv_count.cpu().long(), plan.recv_count)

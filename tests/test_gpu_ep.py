@@ -26,6 +26,7 @@ def test_redundant_physical_experts_under_cuda_graph():
 
 @pytest.mark.parametrize("world,tokens,kw,transport,graph", [
     (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "peer", False),
+    (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "peer-unfused", False),
     (2, (70, 33), dict(zipf_s=1.2, mask_frac=0.05, hot=2), "nccl", False),
     (2, (1, 0), {}, "peer", False),
     (2, (40, 130), dict(zipf_s=1.2, mask_frac=0.05), "peer", True),
@@ -33,6 +34,7 @@ def test_redundant_physical_experts_under_cuda_graph():
 ])
 def test_layer_matches_oracle_at_ep(world, tokens, kw, transport, graph):
     """Per-rank output against the oracle, receive counts / block offsets / statistics bit-exact; with the device-side
-    peer exchange (also replayed from a CUDA graph) and with the host-driven NCCL exchange."""
+    peer exchange (write-back fused into GEMM2, checked bit-identical to the separate copy kernel; also replayed from a
+    CUDA graph) and with the host-driven NCCL exchange."""
     _need(world)
     run_ranks(world, "nccl", layer_body, SMALL, tokens, 3, kw, 1920, transport, graph, timeout=240)

@@ -31,6 +31,8 @@ class KernelOptions:
     engine: int = _native.ENGINE_TENSOR_CORE   # ENGINE_SCALAR_VALIDATION selects the scalar validation kernels (tests)
     ep_transport: str = "peer"  # EP > 1: "peer" = device-side exchange over NVLink peer memory (graph-capturable),
                                 # "nccl" = host-driven all-to-allv (also used when symmetric memory is unavailable)
+    fuse_return: bool = True    # "peer" transport: GEMM2's epilogue stores its rows straight into the source rank's
+                                # buffer over NVLink; False = separate copy kernel after GEMM2 (same result)
 
 
 _kernel_options = KernelOptions()
@@ -236,8 +238,11 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
         peers = (ctypes.c_void_p * sym_buffer.num_ranks)(*sym_buffer.peer_ptrs)
         _native.check(lib.mmoe_ep_dispatch(g, ws, peers, m, ctypes.byref(opts), stream))
         _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
-        _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
-        _native.check(lib.mmoe_ep_return(g, ws, peers, ctypes.byref(opts), stream))
+        if _kernel_options.fuse_return:
+            _native.check(lib.mmoe_experts_ep_return(g, ws, peers, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
+        else:
+            _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
+            _native.check(lib.mmoe_ep_return(g, ws, peers, ctypes.byref(opts), stream))
         _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
         return
     _native.check(lib.mmoe_dispatch_pack(g, ws, m, stream))

@@ -332,8 +332,32 @@ int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_to
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_place launch");
 }
 
+namespace {
+// `peers` != NULL: EP > 1 with the write-back fused into GEMM2, followed by barrier 2
+int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* peers, const MmoeWeights* weights,
+                const MmoeOptions* opt, int32_t num_tokens, int32_t block_m, void* stream);
+}  // namespace
+
 int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  int32_t num_tokens, int32_t block_m, void* stream) {
+  return run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream);
+}
+
+int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces,
+                           const MmoeWeights* weights, const MmoeOptions* opt, int32_t num_tokens, int32_t block_m,
+                           void* stream) {
+  if (geo == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "geometry is NULL");
+  int rc = check_peers(geo, workspace, peer_workspaces);
+  if (rc != MMOE_OK) return rc;
+  if (geo->num_ranks < 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "the fused write-back needs num_ranks > 1");
+  if (opt != nullptr && opt->layer_mask != 0 && opt->layer_mask != 3)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "the fused write-back runs both layers (layer_mask 0 or 3)");
+  return run_experts(geo, workspace, peer_workspaces, weights, opt, num_tokens, block_m, stream);
+}
+
+namespace {
+int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* peers, const MmoeWeights* weights,
+                const MmoeOptions* opt, int32_t num_tokens, int32_t block_m, void* stream) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);
   if (rc != MMOE_OK) return rc;
@@ -357,17 +381,24 @@ int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
   MmoeOptions o = *opt;
   if (o.layer_mask < 0 || o.layer_mask > 3) return fail(MMOE_ERR_INVALID_ARGUMENT, "layer_mask=%d outside [0, 3]", o.layer_mask);
   o.activation_clamp = bf16_round_host(o.activation_clamp);   // the clamp is applied to BF16 values
+  const int64_t timeout_ns = (o.timeout_ms > 0 ? (int64_t)o.timeout_ms : 2000) * 1000000ll;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (o.engine == 1) {
-    e = mmoe::launch_experts_simt(c, *weights, o, num_tokens, block_m, static_cast<cudaStream_t>(stream));
+    // the scalar validation engine writes the local return buffer; the rows then go home with the copy kernel
+    e = mmoe::launch_experts_simt(c, *weights, o, num_tokens, block_m, st);
+    if (e == cudaSuccess && peers != nullptr) e = mmoe::launch_ep_return(c, peers, timeout_ns, st);
   } else if (o.engine == 0) {
     if (!g_prepared) return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() must run before the first launch");
-    e = mmoe::launch_experts_umma(c, *weights, o, num_tokens, block_m, static_cast<cudaStream_t>(stream));
+    c.peer_ws = peers;
+    e = mmoe::launch_experts_umma(c, *weights, o, num_tokens, block_m, st);
+    if (e == cudaSuccess && peers != nullptr) e = mmoe::launch_ep_signal_return(c, peers, timeout_ns, st);
   } else {
     return fail(MMOE_ERR_UNSUPPORTED, "engine=%d", o.engine);
   }
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "experts launch");
 }
+}  // namespace
 
 int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream) {
   mmoe::Ctx c;

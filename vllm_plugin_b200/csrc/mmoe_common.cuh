@@ -163,6 +163,7 @@ struct Ctx {             // resolved pointers of one call
   char* ws;
   int e_local;
   int kmax;              // min(k, E/R)
+  const void* const* peer_ws = nullptr;   // set by the call that fuses the write-back into GEMM2 (EP > 1)
   template <typename T> T* at(int64_t off) const { return reinterpret_cast<T*>(ws + off); }
 };
 
@@ -182,6 +183,8 @@ cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_ex
 int route_order_static_max_tokens();
 int route_order_static_max_experts();
 int ep_sync_bytes();
+int ep_totals_offset();                      // byte offset of the [32][32] route-total table inside the ep_sync region
+cudaError_t launch_ep_signal_return(const Ctx& c, const void* const* peer_ws, int64_t timeout_ns, cudaStream_t s);
 cudaError_t launch_ep_dispatch(const Ctx& c, const void* const* peer_ws, int m, int64_t timeout_ns, cudaStream_t s);
 cudaError_t launch_ep_return(const Ctx& c, const void* const* peer_ws, int64_t timeout_ns, cudaStream_t s);
 

@@ -6,12 +6,15 @@
 //   push      wait flag 0; copy each route's FP8 row, scale words and weight straight from the staged inputs into the
 //             destination rank's receive buffers (receive order = source rank, expert, token, slot) + flag 1
 //   return    after the experts ran: copy every BF16 output row back into its source rank's `ret_recv` at the
-//             source's own send position + flag 2
+//             source's own send position + flag 2; when the GEMM2 epilogue stores its rows straight into the source
+//             rank's `ret_recv` (fused write-back), only the flag is left to do
 //
 // The same exchange exists in the reference as in-kernel NVLink pushes/pulls (backend/kernel/dispatch.py:348-589,
 // epilogue.py:407-413, comm.py:277-318).  Flags are per-call epochs written with release semantics at system scope and
 // read with acquire loads; every wait is bounded and reports through the status words instead of trapping.  No
 // multimem, no TMA from peer memory: plain 16-byte loads and stores only.
+#include <stddef.h>
+
 #include "mmoe_common.cuh"
 
 namespace mmoe {
@@ -198,6 +201,16 @@ __global__ void __launch_bounds__(256) ep_return_kernel(Peers peers, MmoeLayout 
   }
 }
 
+// Fused write-back: the GEMM2 epilogue has already stored every output row into its source rank's `ret_recv`; the
+// kernel boundary completed those stores, so one warp only has to publish barrier 2.
+__global__ void __launch_bounds__(32) ep_signal_kernel(Peers peers, MmoeLayout lay, int num_ranks, int me) {
+  EpSync* sync = reinterpret_cast<EpSync*>(peers.base[me] + lay.ep_sync);
+  const uint32_t epoch = static_cast<uint32_t>(sync->epoch);
+  __threadfence_system();
+  if ((int)threadIdx.x < num_ranks)
+    st_release_sys(&reinterpret_cast<EpSync*>(peers.base[threadIdx.x] + lay.ep_sync)->flags[2][me], epoch);
+}
+
 Peers make_peers(const void* const* peer_ws, int num_ranks) {
   Peers p{};
   for (int i = 0; i < num_ranks; ++i) p.base[i] = static_cast<char*>(const_cast<void*>(peer_ws[i]));
@@ -207,6 +220,8 @@ Peers make_peers(const void* const* peer_ws, int num_ranks) {
 }  // namespace
 
 int ep_sync_bytes() { return static_cast<int>(sizeof(EpSync)); }
+int ep_totals_offset() { return static_cast<int>(offsetof(EpSync, totals)); }
+static_assert(kMaxRanks == 32, "the GEMM2 kernel indexes the totals table as [32][32]");
 
 cudaError_t launch_ep_dispatch(const Ctx& c, const void* const* peer_ws, int m, int64_t timeout_ns, cudaStream_t s) {
   (void)m;
@@ -221,6 +236,13 @@ cudaError_t launch_ep_dispatch(const Ctx& c, const void* const* peer_ws, int m, 
 cudaError_t launch_ep_return(const Ctx& c, const void* const* peer_ws, int64_t timeout_ns, cudaStream_t s) {
   const Peers peers = make_peers(peer_ws, c.geo.num_ranks);
   ep_return_kernel<<<148 * 2, 256, 0, s>>>(peers, c.lay, c.geo.num_ranks, c.geo.rank, c.geo.hidden);
+  ep_wait_kernel<<<1, 32, 0, s>>>(peers, c.lay, c.geo.num_ranks, c.geo.rank, 2, timeout_ns);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_signal_return(const Ctx& c, const void* const* peer_ws, int64_t timeout_ns, cudaStream_t s) {
+  const Peers peers = make_peers(peer_ws, c.geo.num_ranks);
+  ep_signal_kernel<<<1, 32, 0, s>>>(peers, c.lay, c.geo.num_ranks, c.geo.rank);
   ep_wait_kernel<<<1, 32, 0, s>>>(peers, c.lay, c.geo.num_ranks, c.geo.rank, 2, timeout_ns);
   return cudaGetLastError();
 }

@@ -33,7 +33,7 @@ constexpr int kThreads = 224;   // producer, MMA 0, 4 epilogue warps, MMA 1
 constexpr int kSmemBudget = 227 * 1024 - 2048;   // dynamic shared memory we ask for at most (alignment slack excluded)
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitHintNs = 200000;   // upper bound of one hardware-suspended barrier wait (the loop around it re-arms)
-constexpr int kSpinProbes = 0;             // non-blocking probes before a wait may suspend (measured: spinning is slower)
+constexpr int kSpinProbes = 1;             // non-blocking probes before a wait may suspend (more than one is slower)
 
 struct UmmaParams {
   CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 128 rows
@@ -57,6 +57,12 @@ struct UmmaParams {
   __nv_bfloat16* ret;
   __nv_bfloat16* shared_out;
   const int32_t* pool_dst;
+  // layer 2 at EP > 1 with the write-back fused in: an output row goes straight into the `ret_recv` of the rank its
+  // token came from (plain peer stores over NVLink), at that rank's send position
+  int fused_return;
+  int ep_me;
+  const int32_t* ep_totals;    // [32][32]: totals[s][d] = routes rank s sent to rank d in this call
+  __nv_bfloat16* ep_ret_recv[32];
   int32_t* status;
   int64_t timeout_ns;
   int e_local, num_ranks;
@@ -214,6 +220,11 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t a_format, uint32_t n, ui
 #ifndef MMOE_TRACE
 #define MMOE_TRACE 0
 #endif
+// Timing experiments (ablation mask, L2 prefetch distance) are compiled in only on request: their per-stage tests sit
+// in one-thread loops that run at instruction latency.
+#ifndef MMOE_EXPERIMENTS
+#define MMOE_EXPERIMENTS 0
+#endif
 #if MMOE_TRACE
 #define TR_DECL(n) long long n = 0
 #define TR_T0() long long tr_t0 = clock64()
@@ -231,7 +242,14 @@ struct Control {          // lives at the start of shared memory
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   volatile int32_t abort_flag;
+  // layer 2: where output rows go.  slot s < 32: rows of source rank s (slot 0 = the local return buffer when the
+  // write-back is not fused), slot 32: the shared expert's output
+  __nv_bfloat16* out_base[33];
+  int32_t rank_off[33];   // fused write-back: first receive-order row of each source rank
+  int32_t home_base[32];  // ... and the send position on that rank of the first row it sent here
 };
+static_assert(sizeof(Control) <= 1024, "control block");
+constexpr uint32_t kOutSlotShift = 26;   // packed destination: slot << 26 | row
 
 struct Waiter {
   Control* ctl;
@@ -241,6 +259,8 @@ struct Waiter {
   // whole-warp wait: one lane watches the barrier, the others sleep at the warp barrier (a polling warp would put 32
   // requests on the barrier unit per probe and slow the producer and MMA threads that share it)
   __device__ __forceinline__ bool wait_warp(uint32_t bar, uint32_t parity) {
+    // common case: the phase has completed already -- one probe by the whole warp (one broadcast read) and a vote
+    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
     bool ok = true;
     if ((threadIdx.x & 31) == 0) ok = wait(bar, parity);
     return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -325,6 +345,26 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (kLayer == 2) {
+    if (threadIdx.x == 0) {
+      ctl->out_base[32] = p.shared_out;
+      if (!p.fused_return) ctl->out_base[0] = p.ret;
+    }
+    if (p.fused_return) {
+      const int t = threadIdx.x - 32;
+      if (t >= 0 && t < p.num_ranks) {
+        ctl->out_base[t] = p.ep_ret_recv[t];
+        int b = 0;
+        for (int d = 0; d < p.ep_me; ++d) b += p.ep_totals[t * 32 + d];
+        ctl->home_base[t] = b;
+      }
+      if (threadIdx.x == 64) {
+        int run = 0;
+        for (int sr = 0; sr < p.num_ranks; ++sr) { ctl->rank_off[sr] = run; run += p.ep_totals[sr * 32 + p.ep_me]; }
+        ctl->rank_off[p.num_ranks] = run;
+      }
+    }
+  }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                  "r"(kTmemCols)
@@ -346,9 +386,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       uint32_t stage = 0, phase = 0;
       const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
       const uint32_t a0 = smem_u32(a_base), b0 = smem_u32(b_base), sf0 = smem_u32(sf_base);
-      const int ab = p.ablate;
+      const int ab = MMOE_EXPERIMENTS ? p.ablate : 0;
       bool ok = true;
-      TR_DECL(tr_wait); TR_DECL(tr_issue); TR_DECL(tr_iters); TR_T0();
+      TR_DECL(tr_wait); TR_DECL(tr_issue); TR_DECL(tr_iters); TR_DECL(tr_blocked); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
         const int tile_idx = static_cast<int>(task / p.n_blocks);
         const int nb = static_cast<int>(task - (int64_t)tile_idx * p.n_blocks);
@@ -383,6 +423,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         int k0 = 0;
         for (int kb = 0; kb < k_stages; ++kb, k0 += kTileK, wsf += p.rows_per_expert, tsf += tsf_rows) {
           TR_ADD(tr_issue);
+#if MMOE_TRACE
+          if (!mbar_test_wait(empty0 + 8 * stage, phase ^ 1u)) ++tr_blocked;
+#endif
           if (!waiter.wait(empty0 + 8 * stage, phase ^ 1u)) { ok = false; break; }
           TR_ADD(tr_wait);
           const uint32_t bar = full0 + 8 * stage;
@@ -393,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
             if (kLayer == 1) tma_load_5d(a_dst, wmap, k0 / kdiv, 0, group, 0, slice, bar);
             else tma_load_3d(a_dst, wmap, k0 / kdiv, row, slice, bar);
             // ask DRAM for a later K stage of this task now: it needs no shared memory, only L2
-            if (p.prefetch_ahead > 0 && kb + p.prefetch_ahead < k_stages) {
+            if (MMOE_EXPERIMENTS && p.prefetch_ahead > 0 && kb + p.prefetch_ahead < k_stages) {
               if (kLayer == 1) tma_prefetch_5d(wmap, k0 + p.prefetch_ahead * kTileK, 0, group, 0, slice);
               else tma_prefetch_3d(wmap, k0 + p.prefetch_ahead * kTileK, row, slice);
             }
@@ -410,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       }
 #if MMOE_TRACE
       TR_ADD(tr_issue);
-      if (blockIdx.x == 0) printf("L%d producer: iters %lld wait_empty %lld issue %lld\n", kLayer, tr_iters, tr_wait, tr_issue);
+      if (blockIdx.x == 0) printf("L%d producer: iters %lld wait_empty %lld issue %lld blocked %lld\n", kLayer, tr_iters, tr_wait, tr_issue, tr_blocked);
 #endif
     }
   } else if (warp == 1 || warp == 6) {
@@ -435,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
       const uint32_t sfa_col = tmem_base + S::kSfCol + 4 * h;
       const uint32_t sfb_col = tmem_base + S::kSfCol + 8 + 4 * h;
-      const int ab = p.ablate;
+      const int ab = MMOE_EXPERIMENTS ? p.ablate : 0;
       int src[4];                                    // layer 1: source word of the 4 destination words this lane writes
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -444,7 +487,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int r = 16 * ((m & 63) >> 3) + 8 * h + (m & 7);   // stored row inside its 128-row block
         src[t] = 128 * (m >> 6) + 4 * (r & 31) + (r >> 5);
       }
-      TR_DECL(tr_wte); TR_DECL(tr_wfull); TR_DECL(tr_issue); TR_T0();
+      TR_DECL(tr_wte); TR_DECL(tr_wfull); TR_DECL(tr_issue); TR_DECL(tr_blocked); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
         const Tile tile = pv.tiles[task / p.n_blocks];
         const bool shared = tile.expert == kSharedExpert;
@@ -459,9 +502,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const uint32_t sfb = sfb_col + tile.sf_col;
         for (int kb = 0; kb < k_stages; ++kb) {
           TR_ADD(tr_issue);
+#if MMOE_TRACE
+          if (!mbar_test_wait(ready0 + 8 * stage, phase)) ++tr_blocked;
+#endif
           if (!waiter.wait_warp(ready0 + 8 * stage, phase)) { ok = false; break; }
           TR_ADD(tr_wfull);
-          tc_fence_after();
           const uint32_t a_lo = a_lo0 + stage * (S::kABytes >> 4);
           const uint32_t b_lo = b_lo0 + stage * (S::kBBytes >> 4);
           const uint32_t sf_lo = sf_lo0 + stage * (S::kSfBytes >> 4);
@@ -499,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       }
 #if MMOE_TRACE
       TR_ADD(tr_issue);
-      if (blockIdx.x == 0 && lane == 0) printf("L%d mma%d: tasks %u wait_tmem_empty %lld wait_full %lld issue %lld\n", kLayer, h, it, tr_wte, tr_wfull, tr_issue);
+      if (blockIdx.x == 0 && lane == 0) printf("L%d mma%d: tasks %u wait_tmem_empty %lld wait_full %lld issue %lld blocked %lld\n", kLayer, h, it, tr_wte, tr_wfull, tr_issue, tr_blocked);
 #endif
     }
   } else {
@@ -523,7 +568,17 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int i = 32 * c + lane;
         if (i < tile.n_valid) {
           if (kLayer == 1) { if (!shared) wv[c] = __ldg(p.pool_w + tile.row0 + i); }
-          else dv[c] = shared ? tile.row0 + i : __ldg(p.pool_dst + tile.row0 + i);
+          else if (shared) dv[c] = static_cast<int>((32u << kOutSlotShift) | static_cast<uint32_t>(tile.row0 + i));
+          else {
+            const int r = __ldg(p.pool_dst + tile.row0 + i);       // receive-order row
+            if (!p.fused_return) dv[c] = r;
+            else {
+              int sr = 0;
+              while (sr + 1 < p.num_ranks && r >= ctl->rank_off[sr + 1]) ++sr;
+              dv[c] = static_cast<int>((static_cast<uint32_t>(sr) << kOutSlotShift) |
+                                       static_cast<uint32_t>(ctl->home_base[sr] + r - ctl->rank_off[sr]));
+            }
+          }
         }
       }
       TR_ADD(tr_work);
@@ -569,7 +624,6 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int row = nb * 2 * kTileRows + h * kTileRows + q * 32 + lane;     // output feature
-          __nv_bfloat16* out = (shared ? p.shared_out : p.ret) + row;
           for (int i0 = 0; i0 < n16; i0 += 16) {
             uint32_t v[16];
             tc_ld16(d0 + h * S::kNCap + i0, v);
@@ -578,8 +632,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
             const int dcur = c == 0 ? dv[0] : (c == 1 ? dv[1] : (c == 2 ? dv[2] : dv[3]));
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const int dst = __shfl_sync(0xffffffffu, dcur, (i0 & 16) + j);
-              if (i0 + j < tile.n_valid) out[(int64_t)dst * p.hidden] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              const uint32_t dst = static_cast<uint32_t>(__shfl_sync(0xffffffffu, dcur, (i0 & 16) + j));
+              if (i0 + j < tile.n_valid) {
+                __nv_bfloat16* out = ctl->out_base[dst >> kOutSlotShift];
+                out[(int64_t)(dst & ((1u << kOutSlotShift) - 1u)) * p.hidden + row] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              }
             }
           }
         }
@@ -841,6 +898,13 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
   p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
   p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
+  if (c.peer_ws != nullptr && c.geo.num_ranks > 1) {
+    p2.fused_return = 1;
+    p2.ep_me = c.geo.rank;
+    p2.ep_totals = reinterpret_cast<const int32_t*>(c.ws + c.lay.ep_sync + ep_totals_offset());
+    for (int r = 0; r < c.geo.num_ranks; ++r)
+      p2.ep_ret_recv[r] = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(const_cast<void*>(c.peer_ws[r])) + c.lay.ret_recv);
+  }
   p2.k_dim = inter;
   p2.rows_per_expert = h;
   p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
