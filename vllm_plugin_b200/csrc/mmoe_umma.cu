@@ -242,8 +242,8 @@ struct Control {          // lives at the start of shared memory
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   volatile int32_t abort_flag;
-  // layer 2: where output rows go.  slot s < 32: rows of source rank s (slot 0 = the local return buffer when the
-  // write-back is not fused), slot 32: the shared expert's output
+  // layer 2 with the write-back fused in: where output rows go.  slot s < 32: `ret_recv` of source rank s, slot 32: the
+  // shared expert's (local) output
   __nv_bfloat16* out_base[33];
   int32_t rank_off[33];   // fused write-back: first receive-order row of each source rank
   int32_t home_base[32];  // ... and the send position on that rank of the first row it sent here
@@ -314,8 +314,11 @@ struct Shape {
   static_assert(kStages >= 3, "pipeline too shallow");
 };
 
-template <int kLayer, int kBoxRows>
+// kFused (layer 2, EP > 1): every output row goes to the rank its token came from; compiled as kernels of its own so
+// that the single-destination epilogue of the other cases keeps its shorter inner loop.
+template <int kLayer, int kBoxRows, bool kFused = false>
 __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant__ UmmaParams p) {
+  static_assert(!kFused || kLayer == 2, "only GEMM2 writes rows back");
   using S = Shape<kLayer, kBoxRows>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -345,12 +348,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (kLayer == 2) {
-    if (threadIdx.x == 0) {
-      ctl->out_base[32] = p.shared_out;
-      if (!p.fused_return) ctl->out_base[0] = p.ret;
-    }
-    if (p.fused_return) {
+  if (kFused) {
+    if (threadIdx.x == 0) ctl->out_base[32] = p.shared_out;
+    {
       const int t = threadIdx.x - 32;
       if (t >= 0 && t < p.num_ranks) {
         ctl->out_base[t] = p.ep_ret_recv[t];
@@ -568,16 +568,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int i = 32 * c + lane;
         if (i < tile.n_valid) {
           if (kLayer == 1) { if (!shared) wv[c] = __ldg(p.pool_w + tile.row0 + i); }
+          else if (!kFused) dv[c] = shared ? tile.row0 + i : __ldg(p.pool_dst + tile.row0 + i);
           else if (shared) dv[c] = static_cast<int>((32u << kOutSlotShift) | static_cast<uint32_t>(tile.row0 + i));
           else {
             const int r = __ldg(p.pool_dst + tile.row0 + i);       // receive-order row
-            if (!p.fused_return) dv[c] = r;
-            else {
-              int sr = 0;
-              while (sr + 1 < p.num_ranks && r >= ctl->rank_off[sr + 1]) ++sr;
-              dv[c] = static_cast<int>((static_cast<uint32_t>(sr) << kOutSlotShift) |
-                                       static_cast<uint32_t>(ctl->home_base[sr] + r - ctl->rank_off[sr]));
-            }
+            int sr = 0;
+            while (sr + 1 < p.num_ranks && r >= ctl->rank_off[sr + 1]) ++sr;
+            dv[c] = static_cast<int>((static_cast<uint32_t>(sr) << kOutSlotShift) |
+                                     static_cast<uint32_t>(ctl->home_base[sr] + r - ctl->rank_off[sr]));
           }
         }
       }
@@ -620,10 +618,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
           if (lane < 16 && i0 + lane < tile.n_valid)
             sf_out[chunk_pos(tile.sf_col * 32 + i0 + lane) * 4] = static_cast<uint8_t>(my_sf);
         }
-      } else {
+      } else if (!kFused) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int row = nb * 2 * kTileRows + h * kTileRows + q * 32 + lane;     // output feature
+          __nv_bfloat16* out = (shared ? p.shared_out : p.ret) + row;
           for (int i0 = 0; i0 < n16; i0 += 16) {
             uint32_t v[16];
             tc_ld16(d0 + h * S::kNCap + i0, v);
@@ -632,11 +631,29 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
             const int dcur = c == 0 ? dv[0] : (c == 1 ? dv[1] : (c == 2 ? dv[2] : dv[3]));
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const uint32_t dst = static_cast<uint32_t>(__shfl_sync(0xffffffffu, dcur, (i0 & 16) + j));
-              if (i0 + j < tile.n_valid) {
-                __nv_bfloat16* out = ctl->out_base[dst >> kOutSlotShift];
-                out[(int64_t)(dst & ((1u << kOutSlotShift) - 1u)) * p.hidden + row] = __float2bfloat16_rn(__uint_as_float(v[j]));
-              }
+              const int dst = __shfl_sync(0xffffffffu, dcur, (i0 & 16) + j);
+              if (i0 + j < tile.n_valid) out[(int64_t)dst * p.hidden] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+          }
+        }
+      } else {
+        // one destination per token: resolve the 16 row pointers of a batch once, use them for both weight blocks
+        const int row0 = nb * 2 * kTileRows + q * 32 + lane;                      // output feature of weight block 0
+        for (int i0 = 0; i0 < n16; i0 += 16) {
+          uint32_t v0[16], v1[16];
+          tc_ld16(d0 + i0, v0);
+          tc_ld16(d0 + S::kNCap + i0, v1);
+          const int c = i0 >> 5;
+          const int dcur = c == 0 ? dv[0] : (c == 1 ? dv[1] : (c == 2 ? dv[2] : dv[3]));
+          tc_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t dst = static_cast<uint32_t>(__shfl_sync(0xffffffffu, dcur, (i0 & 16) + j));
+            if (i0 + j < tile.n_valid) {
+              __nv_bfloat16* out = ctl->out_base[dst >> kOutSlotShift] +
+                                   (int64_t)(dst & ((1u << kOutSlotShift) - 1u)) * p.hidden + row0;
+              out[0] = __float2bfloat16_rn(__uint_as_float(v0[j]));
+              out[kTileRows] = __float2bfloat16_rn(__uint_as_float(v1[j]));
             }
           }
         }
@@ -756,8 +773,12 @@ int make_packed_map(CUtensorMap* map, bool w13, const void* base, uint64_t k_ele
 
 template <int kLayer, int kBoxRows>
 cudaError_t prepare_one() {
-  return cudaFuncSetAttribute(umma_kernel<kLayer, kBoxRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Shape<kLayer, kBoxRows>::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(umma_kernel<kLayer, kBoxRows, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Shape<kLayer, kBoxRows>::kSmemBytes);
+  if (e == cudaSuccess && kLayer == 2)
+    e = cudaFuncSetAttribute(umma_kernel<2, kBoxRows, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Shape<2, kBoxRows>::kSmemBytes);
+  return e;
 }
 
 template <int kLayer, int kBoxRows>
@@ -767,7 +788,8 @@ cudaError_t launch_one(const UmmaParams& p0, cudaStream_t s) {
   p.num_stages = g_tune_stages > 0 && g_tune_stages < S::kStages ? g_tune_stages : S::kStages;
   p.prefetch_ahead = g_tune_prefetch >= 0 ? g_tune_prefetch : S::kPrefetchAhead;
   p.ablate = g_tune_ablate;
-  umma_kernel<kLayer, kBoxRows><<<g_num_sms, kThreads, S::kSmemBytes, s>>>(p);
+  if (kLayer == 2 && p.fused_return) umma_kernel<2, kBoxRows, true><<<g_num_sms, kThreads, Shape<2, kBoxRows>::kSmemBytes, s>>>(p);
+  else umma_kernel<kLayer, kBoxRows, false><<<g_num_sms, kThreads, S::kSmemBytes, s>>>(p);
   return cudaGetLastError();
 }
 
