@@ -144,7 +144,7 @@ int mmoe_layout(const MmoeGeometry* g, MmoeLayout* out) {
   for (int bm : kBlockMs) {
     const int64_t blocks = max_recv / bm + El;
     pool_rows = blocks * bm > pool_rows ? blocks * bm : pool_rows;
-    const int64_t rows = blocks * ((bm + 127) / 128) * 128;
+    const int64_t rows = blocks * mmoe::chunks_per_block(bm) * 128;
     sf_rows = rows > sf_rows ? rows : sf_rows;
   }
   pool_rows += 128;                              // a tile box may start up to 128 rows before the end of the last block

@@ -15,11 +15,14 @@ constexpr int kGroupK = 32;        // K elements per UE8M0 scale
 constexpr int kTileK = 128;        // K elements per pipeline stage = one packed scale word
 constexpr int kTileRows = 128;     // weight rows per tile (UMMA M)
 constexpr int kChunkRows = 128;    // token rows per scale-factor chunk (one 512-byte tcgen05.cp source per K stage)
-constexpr int kMaxTileTokens = 112;  // largest UMMA N of one task; a fuller chunk is split into two 64-token halves
-// Largest token tile of a BLOCK_M variant.  BLOCK_M = 128 caps its tiles at 80 rows (fuller chunks are split in two):
-// the 10 KB token slot buys a fifth pipeline stage, and at the token counts that select BLOCK_M = 128 a block with
-// more than 80 rows is a 2.6-sigma event.  192 / 240 keep 112.
+constexpr int kMaxTileTokens = 112;  // largest UMMA N of one task
+// Largest token tile of a BLOCK_M variant; an expert with more rows is cut into equal tiles.  BLOCK_M = 128 caps its
+// tiles at 80 rows: the 10 KB token slot buys a fifth pipeline stage.  192 / 240 keep 112 (the tensor-bound
+// expert-parallel shapes, where fewer and larger tiles matter more than pipeline depth).
 __host__ __device__ inline int max_tile_rows(int block_m) { return block_m <= 64 ? block_m : (block_m == 128 ? 80 : kMaxTileTokens); }
+// Scale-factor chunks (128 token rows each) reserved per pool block of a BLOCK_M variant: at least as many as the
+// tiles an expert's rows are cut into (ceil(n / max_tile_rows) <= ceil(n / block_m) * chunks_per_block for every n).
+__host__ __device__ inline int chunks_per_block(int block_m) { return block_m <= 64 ? 1 : (block_m <= 192 ? 2 : 3); }
 constexpr int kSortChunkTokens = 128;
 constexpr int kSharedExpert = -2;  // MmoeTile::expert of a shared-expert tile
 

@@ -344,30 +344,47 @@ cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s) {
 // order (token, slot) -- a fixed order where the reference's is arrival order.
 // =====================================================================================================================
 
-__device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int first_block, bool write) {
-  // tokens [0, n) of one expert laid out in blocks of block_m rows starting at pool block `first_block`
-  const int chunks_per_block = (block_m + kChunkRows - 1) / kChunkRows;
+// Shared expert: the call's own tokens in blocks of block_m rows; the scale chunks were written by the quantiser in the
+// layout the engine prescribes (128-row chunks inside each block, backend/staging.py:85-95), so a tile is one chunk, or
+// one of its two 64-row halves when the chunk holds more rows than a tile may.
+__device__ int emit_shared_tiles(Tile* out, int n, int block_m) {
+  const int cpb = (block_m + kChunkRows - 1) / kChunkRows;
   int count = 0;
   for (int b = 0; b * block_m < n; ++b) {
     const int in_block = min(block_m, n - b * block_m);
-    for (int s = 0; s < chunks_per_block; ++s) {
+    for (int s = 0; s < cpb; ++s) {
       const int rows = min(kChunkRows, in_block - s * kChunkRows);
       if (rows <= 0) break;
-      const int row0 = row_base + b * block_m + s * kChunkRows;
-      const int chunk = (first_block + b) * chunks_per_block + s;
+      const int row0 = b * block_m + s * kChunkRows;
+      const int chunk = b * cpb + s;
       if (rows > max_tile_rows(block_m)) {
-        if (write) {
-          out[count] = Tile{expert, row0, 64, chunk, 0, {0, 0, 0}};
-          out[count + 1] = Tile{expert, row0 + 64, rows - 64, chunk, 2, {0, 0, 0}};
-        }
+        out[count] = Tile{kSharedExpert, row0, 64, chunk, 0, {0, 0, 0}};
+        out[count + 1] = Tile{kSharedExpert, row0 + 64, rows - 64, chunk, 2, {0, 0, 0}};
         count += 2;
       } else {
-        if (write) out[count] = Tile{expert, row0, rows, chunk, 0, {0, 0, 0}};
+        out[count] = Tile{kSharedExpert, row0, rows, chunk, 0, {0, 0, 0}};
         count += 1;
       }
     }
   }
   return count;
+}
+
+// Routed expert: its n rows are contiguous in the pool, starting on a block_m boundary (pool block `first_block`).
+// They are cut into ceil(n / max_tile_rows) equal tiles (rounded up to 16 rows) regardless of the block boundaries
+// inside the expert.  The scale chunks of the pool are this library's own: tile j of the expert uses chunk j of the
+// chunks reserved for the expert's blocks.
+__device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int first_block, bool write) {
+  if (n <= 0) return 0;
+  const int cap = max_tile_rows(block_m);
+  const int parts = (n + cap - 1) / cap;
+  const int step = parts == 1 ? n : ((n + parts - 1) / parts + 15) & ~15;
+  if (write) {
+    const int chunk0 = first_block * chunks_per_block(block_m);
+    for (int j = 0; j < parts; ++j)
+      out[j] = Tile{expert, row_base + j * step, min(step, n - j * step), chunk0 + j, 0, {0, 0, 0}};
+  }
+  return parts;
 }
 
 __global__ void __launch_bounds__(1024) plan_kernel(
@@ -407,7 +424,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(
     pv.hdr->num_tokens = m;
     // shared-expert tiles: the call's own tokens in blocks of block_m (chunk numbering of backend/staging.py:85-95)
     int ns = 0;
-    if (has_shared) ns = emit_tiles(pv.tiles + rt, kSharedExpert, 0, m, block_m, 0, true);
+    if (has_shared) ns = emit_shared_tiles(pv.tiles + rt, m, block_m);
     pv.hdr->num_shared_tiles = ns;
   }
   __syncthreads();
@@ -474,7 +491,7 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     pv.hdr->total_recv = off[num_experts];
     pv.hdr->block_m = block_m;
     pv.hdr->num_tokens = m;
-    pv.hdr->num_shared_tiles = has_shared ? emit_tiles(pv.tiles + to, kSharedExpert, 0, m, block_m, 0, true) : 0;
+    pv.hdr->num_shared_tiles = has_shared ? emit_shared_tiles(pv.tiles + to, m, block_m) : 0;
     pv.rank_off[0] = 0;
     pv.rank_off[1] = off[num_experts];
   }
