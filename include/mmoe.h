@@ -189,6 +189,15 @@ int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t
 int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream);
 
+/* EP>1 convenience, device-side transport: count, exchange, place, experts with the fused write-back, combine.  The
+ * exchange of counts and rows runs on a second stream of the library (created by `mmoe_prepare`) while the shared
+ * expert, which needs only this rank's own tokens, runs both of its GEMMs on `stream`; the two streams fork and join
+ * with events, so the whole call can be captured in a CUDA graph.  Same result as the separate calls.  Corresponds to
+ * the reference scheduling the shared expert into the dispatch gap (backend/kernel/scheduler.py:250-259). */
+int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces,
+                    const MmoeWeights* weights, const MmoeOptions* opt, void* y_bf16, int32_t num_tokens, int32_t block_m,
+                    int32_t* stats, void* stream);
+
 /* Copy the device status words to the host (synchronises the stream) and translate them: MMOE_OK or
  * MMOE_ERR_DEVICE_TIMEOUT.  Replaces the reference's device `trap` after a 300 s spin (backend/kernel/comm.py:229-250). */
 int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream);

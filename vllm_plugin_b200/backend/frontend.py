@@ -32,7 +32,8 @@ class KernelOptions:
     ep_transport: str = "peer"  # EP > 1: "peer" = device-side exchange over NVLink peer memory (graph-capturable),
                                 # "nccl" = host-driven all-to-allv (also used when symmetric memory is unavailable)
     fuse_return: bool = True    # "peer" transport: GEMM2's epilogue stores its rows straight into the source rank's
-                                # buffer over NVLink; False = separate copy kernel after GEMM2 (same result)
+                                # buffer over NVLink, and the dispatch overlaps the shared expert's GEMMs on a second
+                                # stream; False = one stream, separate copy kernel after GEMM2 (same result)
 
 
 _kernel_options = KernelOptions()
@@ -232,19 +233,21 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
         _native.check(lib.mmoe_forward(g, ws, ctypes.byref(w), ctypes.byref(opts), y.data_ptr(), m, bm, stats_ptr, stream))
         return
     group = sym_buffer.group
-    _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
     if sym_buffer.peer_ptrs is not None and _kernel_options.ep_transport == "peer":
         # device-side exchange: no host round trip, capturable in a CUDA graph
         peers = (ctypes.c_void_p * sym_buffer.num_ranks)(*sym_buffer.peer_ptrs)
+        if _kernel_options.fuse_return:
+            _native.check(lib.mmoe_forward_ep(g, ws, peers, ctypes.byref(w), ctypes.byref(opts), y.data_ptr(), m, bm,
+                                              stats_ptr, stream))
+            return
+        _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
         _native.check(lib.mmoe_ep_dispatch(g, ws, peers, m, ctypes.byref(opts), stream))
         _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
-        if _kernel_options.fuse_return:
-            _native.check(lib.mmoe_experts_ep_return(g, ws, peers, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
-        else:
-            _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
-            _native.check(lib.mmoe_ep_return(g, ws, peers, ctypes.byref(opts), stream))
+        _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
+        _native.check(lib.mmoe_ep_return(g, ws, peers, ctypes.byref(opts), stream))
         _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
         return
+    _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
     _native.check(lib.mmoe_dispatch_pack(g, ws, m, stream))
     send_splits, recv_splits = exchange_counts(group, sym_buffer.send_count, sym_buffer.recv_count)
     exchange_rows(group, sym_buffer.recv_x, sym_buffer.send_x, recv_splits, send_splits)

@@ -30,6 +30,29 @@ int cuda_fail(cudaError_t e, const char* what) {
 const int kBlockMs[6] = {16, 32, 64, 128, 192, 240};
 bool g_prepared = false;
 
+// A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.
+struct SideLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+constexpr int kMaxDevices = 64;
+SideLane g_side[kMaxDevices];
+
+SideLane* side_lane(bool may_create) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  SideLane& l = g_side[dev];
+  if (l.stream == nullptr && may_create) {
+    SideLane n;
+    if (cudaStreamCreateWithFlags(&n.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&n.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&n.join, cudaEventDisableTiming) != cudaSuccess)
+      return nullptr;
+    l = n;
+  }
+  return l.stream != nullptr ? &l : nullptr;
+}
+
 bool valid_block_m(int bm) {
   for (int v : kBlockMs)
     if (v == bm) return true;
@@ -149,7 +172,7 @@ int mmoe_layout(const MmoeGeometry* g, MmoeLayout* out) {
   }
   pool_rows += 128;                              // a tile box may start up to 128 rows before the end of the last block
   const int64_t shared_rows = (T + 7) / 8 * 128;
-  const int64_t max_tiles = (max_recv / 16 + El) * 2 + (T / 16 + 2) * 2;
+  const int64_t max_tiles = (max_recv / 16 + El) * 2 + mmoe::shared_tile_capacity(T);
   const bool ep = R > 1;
   const bool shared = g->num_shared_experts > 0;
 
@@ -215,6 +238,7 @@ int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_
   rc = mmoe::prepare_umma(*geo);
   if (rc != MMOE_OK) return fail(rc, "loading the tensor-core kernels failed: %s", cudaGetErrorString(cudaGetLastError()));
   g_prepared = true;
+  if (geo->num_ranks > 1) side_lane(true);      // streams and events cannot be created while a stream is capturing
   // every BLOCK_M the geometry can select for M in [0, T]
   bool seen[6] = {false, false, false, false, false, false};
   for (int m = 0; m <= geo->num_max_tokens; ++m) {
@@ -335,7 +359,8 @@ int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_to
 namespace {
 // `peers` != NULL: EP > 1 with the write-back fused into GEMM2, followed by barrier 2
 int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* peers, const MmoeWeights* weights,
-                const MmoeOptions* opt, int32_t num_tokens, int32_t block_m, void* stream);
+                const MmoeOptions* opt, int32_t num_tokens, int32_t block_m, void* stream, int tile_select = 0);
+
 }  // namespace
 
 int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
@@ -357,7 +382,7 @@ int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void*
 
 namespace {
 int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* peers, const MmoeWeights* weights,
-                const MmoeOptions* opt, int32_t num_tokens, int32_t block_m, void* stream) {
+                const MmoeOptions* opt, int32_t num_tokens, int32_t block_m, void* stream, int tile_select) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);
   if (rc != MMOE_OK) return rc;
@@ -391,6 +416,7 @@ int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* pee
   } else if (o.engine == 0) {
     if (!g_prepared) return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() must run before the first launch");
     c.peer_ws = peers;
+    c.tile_select = tile_select;
     e = mmoe::launch_experts_umma(c, *weights, o, num_tokens, block_m, st);
     if (e == cudaSuccess && peers != nullptr) e = mmoe::launch_ep_signal_return(c, peers, timeout_ns, st);
   } else {
@@ -430,6 +456,50 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
     if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
   }
   if (rc == MMOE_OK) rc = mmoe_experts(geo, workspace, weights, opt, num_tokens, block_m, stream);
+  if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+  return rc;
+}
+
+int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces,
+                    const MmoeWeights* weights, const MmoeOptions* opt, void* y_bf16, int32_t num_tokens, int32_t block_m,
+                    int32_t* stats, void* stream) {
+  if (geo == nullptr || opt == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "geometry / options are NULL");
+  if (geo->num_ranks < 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "mmoe_forward_ep is the num_ranks > 1 sequence");
+  int rc = check_peers(geo, workspace, peer_workspaces);
+  if (rc == MMOE_OK) rc = mmoe_dispatch_count(geo, workspace, num_tokens, stream);
+  if (rc != MMOE_OK) return rc;
+  cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(main_stream, &cap);
+  SideLane* lane = nullptr;
+  if (opt->engine == 0 && geo->num_shared_experts > 0 && num_tokens > 0)
+    lane = side_lane(cap == cudaStreamCaptureStatusNone);
+  if (lane == nullptr) {
+    // nothing to overlap (no shared expert, no tokens here, validation engine): one stream
+    rc = mmoe_ep_dispatch(geo, workspace, peer_workspaces, num_tokens, opt, stream);
+    if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
+    if (rc == MMOE_OK) rc = run_experts(geo, workspace, peer_workspaces, weights, opt, num_tokens, block_m, stream, 0);
+    if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+    return rc;
+  }
+  // fork: the exchange of counts and rows runs on the side stream ...
+  cudaError_t e = cudaEventRecord(lane->fork, main_stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(lane->stream, lane->fork, 0);
+  if (e != cudaSuccess) return cuda_fail(e, "forking the dispatch stream");
+  const int rc_side = mmoe_ep_dispatch(geo, workspace, peer_workspaces, num_tokens, opt, lane->stream);
+  e = cudaEventRecord(lane->join, lane->stream);
+  // ... while the shared expert, which needs only this rank's own tokens, runs both of its GEMMs here
+  mmoe::Ctx c;
+  rc = make_ctx(geo, workspace, &c);
+  if (rc == MMOE_OK && mmoe::launch_shared_plan(c, num_tokens, block_m, main_stream) != cudaSuccess)
+    rc = cuda_fail(cudaGetLastError(), "shared plan launch");
+  if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 2);
+  // join (always, so that a capture is never left forked)
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(main_stream, lane->join, 0);
+  if (e != cudaSuccess) return cuda_fail(e, "joining the dispatch stream");
+  if (rc_side != MMOE_OK) return rc_side;
+  if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
+  if (rc == MMOE_OK) rc = run_experts(geo, workspace, peer_workspaces, weights, opt, num_tokens, block_m, stream, 1);
   if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
   return rc;
 }

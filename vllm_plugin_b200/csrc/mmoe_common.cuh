@@ -46,7 +46,8 @@ struct PlanHeader {
   int32_t total_recv;          // routes received by this rank
   int32_t block_m;
   int32_t num_tokens;
-  int32_t pad[10];
+  int32_t num_early_shared_tiles;   // shared-expert tiles written ahead of the routed plan, at the tail of the tile table
+  int32_t pad[9];
 };
 static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
 
@@ -64,6 +65,10 @@ struct PlanView {
 };
 
 __host__ __device__ inline int64_t align_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+// tile records reserved for the shared expert of a call with at most `max_tokens` tokens (they sit at the tail of the
+// tile table when the shared expert is planned ahead of the routed experts)
+__host__ __device__ inline int64_t shared_tile_capacity(int64_t max_tokens) { return (max_tokens / 16 + 2) * 2; }
 
 __host__ __device__ inline int64_t plan_bytes(int e_local, int num_ranks, int64_t max_tiles) {
   int64_t ints = e_local + 2 * (e_local + 1) + (num_ranks + 1) + 2 * (int64_t)e_local * num_ranks;
@@ -167,6 +172,7 @@ struct Ctx {             // resolved pointers of one call
   int e_local;
   int kmax;              // min(k, E/R)
   const void* const* peer_ws = nullptr;   // set by the call that fuses the write-back into GEMM2 (EP > 1)
+  int tile_select = 0;                    // 0: every tile of the plan, 1: routed tiles only, 2: the early shared tiles only
   template <typename T> T* at(int64_t off) const { return reinterpret_cast<T*>(ws + off); }
 };
 
@@ -176,6 +182,7 @@ cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
 cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
+cudaError_t launch_shared_plan(const Ctx& c, int m, int block_m, cudaStream_t s);
 cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s);
 cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);

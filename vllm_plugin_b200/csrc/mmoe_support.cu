@@ -387,6 +387,16 @@ __device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_
   return parts;
 }
 
+// The shared expert's tiles depend only on the token count, so they can be planned (and run) before the routed
+// experts' receive counts are known: written at the tail of the tile table, counted in the header.
+__global__ void shared_plan_kernel(char* __restrict__ plan_base, int e_local, int num_ranks, int m, int block_m,
+                                   int64_t first_tile) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    PlanView pv = plan_view(plan_base, e_local, num_ranks);
+    pv.hdr->num_early_shared_tiles = emit_shared_tiles(pv.tiles + first_tile, m, block_m);
+  }
+}
+
 __global__ void __launch_bounds__(1024) plan_kernel(
     char* __restrict__ plan_base, const int32_t* __restrict__ recv_count, int32_t* __restrict__ stats, int e_local,
     int num_ranks, int block_m, int m, int has_shared) {
@@ -587,6 +597,12 @@ cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int3
       c.at<int32_t>(c.lay.sorted_route), c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf),
       c.at<float>(c.lay.pool_w), c.at<int32_t>(c.lay.pool_dst), c.lay.pool_sf_rows, c.e_local, 1, c.geo.hidden,
       c.geo.num_topk, 1);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_shared_plan(const Ctx& c, int m, int block_m, cudaStream_t s) {
+  shared_plan_kernel<<<1, 32, 0, s>>>(c.ws + c.lay.plan, c.e_local, c.geo.num_ranks, m, block_m,
+                                      c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens));
   return cudaGetLastError();
 }
 

@@ -59,6 +59,8 @@ struct UmmaParams {
   const int32_t* pool_dst;
   // layer 2 at EP > 1 with the write-back fused in: an output row goes straight into the `ret_recv` of the rank its
   // token came from (plain peer stores over NVLink), at that rank's send position
+  int tile_select;             // 0: every tile of the plan, 1: routed tiles only, 2: the early shared tiles only
+  int64_t early_shared_first;  // index of the first early shared tile in the tile table
   int fused_return;
   int ep_me;
   const int32_t* ep_totals;    // [32][32]: totals[s][d] = routes rank s sent to rank d in this call
@@ -330,8 +332,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
-  const int num_routed = pv.hdr->num_routed_tiles;
-  const int num_tiles = num_routed + (p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
+  const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
+  const int num_tiles = p.tile_select == 2
+                            ? (p.has_shared_weights ? pv.hdr->num_early_shared_tiles : 0)
+                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
   const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
   const int k_stages = p.k_dim / kTileK;
   const uint32_t num_stages = static_cast<uint32_t>(p.num_stages);
@@ -392,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
         const int tile_idx = static_cast<int>(task / p.n_blocks);
         const int nb = static_cast<int>(task - (int64_t)tile_idx * p.n_blocks);
-        const Tile tile = pv.tiles[tile_idx];
+        const Tile tile = tiles[tile_idx];
         const bool shared = tile.expert == kSharedExpert;
         // smallest token box that covers the tile (16 / 32 / 64 / 128 rows): fewer rows to move and to pad
         const int n16 = (tile.n_valid + 15) & ~15;
@@ -489,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       }
       TR_DECL(tr_wte); TR_DECL(tr_wfull); TR_DECL(tr_issue); TR_DECL(tr_blocked); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
-        const Tile tile = pv.tiles[task / p.n_blocks];
+        const Tile tile = tiles[task / p.n_blocks];
         const bool shared = tile.expert == kSharedExpert;
         const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
         TR_ADD(tr_issue);
@@ -555,7 +559,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     bool ok = true;
     TR_DECL(tr_wfull); TR_DECL(tr_work); TR_T0();
     for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
-      const Tile tile = pv.tiles[task / p.n_blocks];
+      const Tile tile = tiles[task / p.n_blocks];
       const int nb = static_cast<int>(task % p.n_blocks);
       const bool shared = tile.expert == kSharedExpert;
       const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
@@ -895,6 +899,8 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p1.clamp = o.activation_clamp;
   p1.fast_math = o.fast_math;
   p1.has_shared_weights = has_shared ? 1 : 0;
+  p1.tile_select = c.tile_select;
+  p1.early_shared_first = c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens);
 
   UmmaParams p2 = p1;
   bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
@@ -920,7 +926,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
   p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
   p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
-  if (c.peer_ws != nullptr && c.geo.num_ranks > 1) {
+  if (c.peer_ws != nullptr && c.geo.num_ranks > 1 && c.tile_select != 2) {
     p2.fused_return = 1;
     p2.ep_me = c.geo.rank;
     p2.ep_totals = reinterpret_cast<const int32_t*>(c.ws + c.lay.ep_sync + ep_totals_offset());
