@@ -48,6 +48,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
+// one warp copies a row of `vec` 16-byte vectors, four loads in flight per lane
+__device__ __forceinline__ void copy_row(uint4* __restrict__ dst, const uint4* __restrict__ src, int vec, int lane) {
+  for (int v0 = lane; v0 < vec; v0 += 128) {
+    uint4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (v0 + 32 * u < vec) q[u] = src[v0 + 32 * u];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (v0 + 32 * u < vec) dst[v0 + 32 * u] = q[u];
+  }
+}
+
 // thread s < R waits until rank s has passed barrier `b` of epoch `epoch`; bounded
 __device__ void wait_flags(EpSync* sync, int b, int num_ranks, uint32_t epoch, int64_t timeout_ns, int32_t* status) {
   if ((int)threadIdx.x < num_ranks) {
@@ -137,7 +150,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(Peers peers, MmoeLayout la
     const int t = route / k;
     char* peer = peers.base[d];
     uint4* dx = reinterpret_cast<uint4*>(peer + lay.recv_x) + row * vec;
-    for (int v = lane; v < vec; v += 32) dx[v] = x[(int64_t)t * vec + v];
+    copy_row(dx, x + (int64_t)t * vec, vec, lane);
     int32_t* dsf = reinterpret_cast<int32_t*>(peer + lay.recv_sf) + row * words;
     for (int w = lane; w < words; w += 32) dsf[w] = x_sf[(int64_t)t * words + w];
     if (lane == 0) reinterpret_cast<float*>(peer + lay.recv_w)[row] = topk_w[route];
@@ -188,7 +201,7 @@ __global__ void __launch_bounds__(256) ep_return_kernel(Peers peers, MmoeLayout 
     while (r >= rank_off[s + 1]) ++s;
     const int64_t row = home_base[s] + (r - rank_off[s]);
     uint4* dst = reinterpret_cast<uint4*>(peers.base[s] + lay.ret_recv) + row * vec;
-    for (int v = lane; v < vec; v += 32) dst[v] = ret[(int64_t)r * vec + v];
+    copy_row(dst, ret + (int64_t)r * vec, vec, lane);
   }
   __threadfence_system();
   __syncthreads();

@@ -539,7 +539,9 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
 }
 
 // Place: one warp per pool row of every routed tile: copy the FP8 row, scatter its scale words into the chunk layout,
-// record the top-k weight and the receive-order row that takes the expert output.
+// record the top-k weight and the receive-order row that takes the expert output.  A block takes 32 rows of a tile at a
+// time (a tile has at most 4 such slices), so the grid stays busy whatever the number of tiles, and every lane keeps
+// four 16-byte loads in flight.
 __global__ void __launch_bounds__(256) place_kernel(
     char* __restrict__ plan_base, const uint4* __restrict__ src_x, const int32_t* __restrict__ src_sf,
     const float* __restrict__ src_w, const int32_t* __restrict__ sorted_route, uint4* __restrict__ pool_x,
@@ -550,11 +552,15 @@ __global__ void __launch_bounds__(256) place_kernel(
   const int block_m = pv.hdr->block_m;
   const int vec = h / 16, words = h / kTileK;
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+  constexpr int kSlices = (kMaxTileTokens + 31) / 32;
+  for (int task = blockIdx.x; task < ntiles * kSlices; task += gridDim.x) {
+    const int slice = task / ntiles, t = task - slice * ntiles;   // slice-major: the first slices are the populated ones
     const Tile tile = pv.tiles[t];
+    const int i_end = min(tile.n_valid, 32 * slice + 32);
+    if (32 * slice >= i_end) continue;
     const int e = tile.expert;
     const int expert_row0 = pv.expert_block_off[e] * block_m;
-    for (int i = warp_in_block; i < tile.n_valid; i += warps) {
+    for (int i = 32 * slice + warp_in_block; i < i_end; i += warps) {
       const int p = tile.row0 + i;
       const int j = p - expert_row0;           // index of this row among the expert's routes
       int r = 0, acc = 0;
@@ -573,7 +579,17 @@ __global__ void __launch_bounds__(256) place_kernel(
       } else {
         w = src_w[recv_row];
       }
-      for (int v = lane; v < vec; v += 32) pool_x[(int64_t)p * vec + v] = src_x[src_row * vec + v];
+      const uint4* src = src_x + src_row * vec;
+      uint4* dst = pool_x + (int64_t)p * vec;
+      for (int v0 = lane; v0 < vec; v0 += 128) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + 32 * u < vec) q[u] = src[v0 + 32 * u];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + 32 * u < vec) dst[v0 + 32 * u] = q[u];
+      }
       const int pos = tile.sf_chunk * kChunkRows + chunk_pos(tile.sf_col * 32 + i);
       for (int wd = lane; wd < words; wd += 32) pool_sf[(int64_t)wd * pool_sf_rows + pos] = src_sf[src_row * words + wd];
       if (lane == 0) {
@@ -611,7 +627,7 @@ cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, 
   plan_kernel<<<1, 1024, 0, s>>>(c.ws + c.lay.plan, c.at<int32_t>(c.lay.recv_count), stats, c.e_local, R, block_m, m,
                                  c.geo.num_shared_experts > 0);
   const bool direct = R == 1;
-  place_kernel<<<148 * 4, 256, 0, s>>>(
+  place_kernel<<<148 * 8, 256, 0, s>>>(
       c.ws + c.lay.plan, direct ? c.at<uint4>(c.lay.x) : c.at<uint4>(c.lay.recv_x),
       direct ? c.at<int32_t>(c.lay.x_sf) : c.at<int32_t>(c.lay.recv_sf),
       direct ? c.at<float>(c.lay.topk_weights) : c.at<float>(c.lay.recv_w), c.at<int32_t>(c.lay.sorted_route),
