@@ -53,8 +53,9 @@ def test_small_layer_matches_oracle(engine, m, shared):
 
 @pytest.mark.parametrize("bm", [16, 32, 64, 128, 192, 240])
 def test_every_block_m_variant(bm):
-    """Forced BLOCK_M with ~150 tokens per expert: several blocks per expert, partially filled last blocks, and for
-    BLOCK_M >= 128 chunks of more than 112 rows that are split into two tensor-core tiles."""
+    """Forced BLOCK_M with ~150 tokens per expert (Zipf: some experts far more): several pool blocks per expert,
+    partially filled last blocks, and experts whose rows are cut into two or more equal tensor-core tiles that do not
+    follow the block boundaries."""
     from vllm_plugin_b200 import api
     layer = H.make_layer(shared=True, seed=3, **SMALL)
     m = 600
