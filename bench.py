@@ -305,7 +305,7 @@ def run_ours(args):
         ach = w13_bytes / (g1_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "umma_kernel<1> (grouped GEMM1 + SwiGLU/requant)", "achieved": ach,
                     "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": f"of {peak_kind}",
-                    # DRAM bytes per launch: ncu read+write of this kernel on the E=64 capture (profiles/) was 1.059x its
+                    # DRAM bytes per launch: ncu read+write of this kernel on the E=64 capture (profiles/) was 1.056x its
                     # algorithmic bytes; traffic grows with the experts hit, so the same ratio is applied here
                     "traffic": w13_bytes * NCU_TRAFFIC_RATIO_GEMM1, "traffic_source": "scaled from the E=64, M=640 ncu capture by the experts hit",
                     "algorithmic_bytes_per_launch": w13_bytes, "ms_per_launch": g1_ms}
@@ -354,6 +354,24 @@ def run_ours(args):
         line_extra["sweep"] = sweep
         if "64" in sweep:
             line_extra["p50_us_at_M64"] = sweep["64"]["p50_us"]
+
+        # ---- load-time weight transform (checkpoint row order -> kernel layout) of all routed W13: read once, written once
+        if not args.no_sweep:
+            pair = (syn.l1[0], syn.l1[1])
+            api.transform_weights_for_mega_moe(pair, (syn.l2[0], syn.l2[1]))     # warm-up
+            tt = []
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                out = api.transform_weights_for_mega_moe(pair, (syn.l2[0], syn.l2[1]))
+                e1.record(stream)
+                torch.cuda.synchronize(dev)
+                tt.append(e0.elapsed_time(e1))
+                del out
+            moved = 2 * (syn.l1[0].numel() + syn.l1[1].numel() * 4 + syn.l2[1].numel() * 4)
+            t_ms = statistics.median(tt)
+            line_extra["weight_transform"] = {"ms": t_ms, "bytes_read_plus_written": moved, "gbs": moved / (t_ms * 1e-3) / 1e9,
+                                              "hbm_frac": moved / (t_ms * 1e-3) / 1e9 / peak}
 
     from vllm_plugin_b200.backend.frontend import read_status
     read_status(buf)

@@ -198,6 +198,16 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
                     const MmoeWeights* weights, const MmoeOptions* opt, void* y_bf16, int32_t num_tokens, int32_t block_m,
                     int32_t* stats, void* stream);
 
+/* Load-time transform of one (weights, scale factors) pair into the layout the grouped GEMMs read; replaces the torch
+ * indexing ops of `transform_weights_for_mega_moe` (backend/weights.py:83-145) with two HBM-bound kernels, bit for bit.
+ * `w_in` / `w_out`: `num_groups` matrices of `rows` x `k_packed_bytes` bytes (packed FP4 or FP8), contiguous; `sf_in` /
+ * `sf_out`: int32 scale words, MN-major `[num_groups][k_words][rows]` (rows % 128 == 0, dense).  `interleave` = 1 (W13):
+ * rows `[gate | up]` -> `[g0..7, u0..7, g8..15, ...]` for weights and scales, then the 4x32 transpose of the scale words
+ * inside every 128-row block; `interleave` = 0 (W2): only the scale transpose, `w_in` / `w_out` are not touched and may
+ * be NULL.  Out of place. */
+int mmoe_transform_weights(const void* w_in, void* w_out, const int32_t* sf_in, int32_t* sf_out, int32_t num_groups,
+                           int32_t rows, int32_t k_packed_bytes, int32_t k_words, int32_t interleave, void* stream);
+
 /* Copy the device status words to the host (synchronises the stream) and translate them: MMOE_OK or
  * MMOE_ERR_DEVICE_TIMEOUT.  Replaces the reference's device `trap` after a 300 s spin (backend/kernel/comm.py:229-250). */
 int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream);

@@ -29,7 +29,7 @@ EXPORTED_SYMBOLS = (
     "mmoe_layout", "mmoe_block_m", "mmoe_prepare", "mmoe_stage_inputs", "mmoe_dispatch_count", "mmoe_dispatch_pack",
     "mmoe_dispatch_place", "mmoe_experts", "mmoe_combine", "mmoe_forward", "mmoe_read_status", "mmoe_status_string",
     "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc", "mmoe_ep_dispatch", "mmoe_ep_return",
-    "mmoe_experts_ep_return", "mmoe_forward_ep",
+    "mmoe_experts_ep_return", "mmoe_forward_ep", "mmoe_transform_weights",
 )
 
 
@@ -101,6 +101,7 @@ def load() -> ctypes.CDLL:
     lib.mmoe_ep_return.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeOptions), vp]
     lib.mmoe_forward_ep.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeWeights), ctypes.POINTER(MmoeOptions),
                                     vp, i32, i32, vp, vp]
+    lib.mmoe_transform_weights.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.mmoe_experts_ep_return.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeWeights),
                                            ctypes.POINTER(MmoeOptions), i32, i32, vp]
     lib.mmoe_route_order_noalloc.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]

@@ -96,6 +96,33 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
         assert sf.dtype == torch.int32, "scale factors must be packed int32 words"
         assert sf.stride(-2) == 1, "scale factors must be MN-major (stride(-2) == 1)"
         assert w.shape[-2] == sf.shape[-2], "weights and scale factors disagree on the row count"
+    if l1_weights[0].is_cuda and _native_transform_applies(l1_weights) and _native_transform_applies(l2_weights):
+        # device tensors: two HBM-bound CUDA kernels per pair (bit-identical to the indexing ops below)
+        return ((_native_transform(l1_weights, True)), (l2_weights[0], _native_transform(l2_weights, False)[1]))
     l1 = (interleave_weights(l1_weights[0]), transpose_sf_for_utccp(interleave_weights(l1_weights[1])))
     l2 = (l2_weights[0], transpose_sf_for_utccp(l2_weights[1]))
     return l1, l2
+
+
+def _native_transform_applies(pair: Tuple[torch.Tensor, torch.Tensor]) -> bool:
+    w, sf = pair
+    rows = w.shape[-2]
+    dense = sf.stride(-1) == rows and (sf.dim() == 2 or sf.stride(0) == rows * sf.shape[-1])
+    return (w.is_cuda and sf.is_cuda and w.is_contiguous() and w.element_size() == 1 and rows % 128 == 0
+            and w.shape[-1] % 16 == 0 and dense and w.data_ptr() % 16 == 0 and sf.data_ptr() % 16 == 0)
+
+
+def _native_transform(pair: Tuple[torch.Tensor, torch.Tensor], interleave: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    from . import _native
+    w, sf = pair
+    groups = w.shape[0] if w.dim() == 3 else 1
+    rows, row_bytes, k_words = w.shape[-2], w.shape[-1], sf.shape[-1]
+    w_out = torch.empty_like(w) if interleave else w
+    sf_out = torch.empty_like(sf)                      # keeps the MN-major strides
+    assert sf_out.stride() == sf.stride()
+    stream = torch.cuda.current_stream(w.device).cuda_stream
+    with torch.cuda.device(w.device):
+        _native.check(_native.load().mmoe_transform_weights(
+            w.data_ptr() if interleave else None, w_out.data_ptr() if interleave else None, sf.data_ptr(),
+            sf_out.data_ptr(), groups, rows, row_bytes, k_words, 1 if interleave else 0, stream))
+    return w_out, sf_out

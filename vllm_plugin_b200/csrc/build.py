@@ -13,7 +13,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(os.path.dirname(HERE), "_lib")
-SOURCES = ("mmoe_abi.cu", "mmoe_support.cu", "mmoe_umma.cu", "mmoe_ep.cu")
+SOURCES = ("mmoe_abi.cu", "mmoe_support.cu", "mmoe_umma.cu", "mmoe_ep.cu", "mmoe_weights.cu")
 LIB_NAME = "libmmoe_b200.so"
 
 

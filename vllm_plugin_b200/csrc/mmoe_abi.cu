@@ -504,6 +504,26 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   return rc;
 }
 
+int mmoe_transform_weights(const void* w_in, void* w_out, const int32_t* sf_in, int32_t* sf_out, int32_t num_groups,
+                           int32_t rows, int32_t k_packed_bytes, int32_t k_words, int32_t interleave, void* stream) {
+  if (num_groups <= 0 || rows <= 0 || k_packed_bytes <= 0 || k_words <= 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: sizes must be positive");
+  if (rows % 128 != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: rows=%d is not a multiple of 128", rows);
+  if (interleave && rows % 16 != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: gate/up interleave needs rows %% 16 == 0");
+  if (k_packed_bytes % 16 != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: a weight row must be a multiple of 16 bytes");
+  if (sf_in == nullptr || sf_out == nullptr || sf_in == sf_out) return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: scale pointers must be distinct and non-NULL");
+  if (interleave && (w_in == nullptr || w_out == nullptr || w_in == w_out))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: weight pointers must be distinct and non-NULL when rows are interleaved");
+  const void* ptrs[] = {w_in, w_out, sf_in, sf_out};
+  for (const void* p : ptrs)
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "transform: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+  if (interleave) e = mmoe::launch_interleave_rows(w_in, w_out, num_groups, rows, k_packed_bytes, st);
+  if (e == cudaSuccess) e = mmoe::launch_scale_layout(sf_in, sf_out, num_groups, rows, rows, k_words, interleave, st);
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "weight transform launch");
+}
+
 int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);

@@ -192,6 +192,9 @@ cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_ex
                                int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route, cudaStream_t s);
 int route_order_static_max_tokens();
 int route_order_static_max_experts();
+cudaError_t launch_interleave_rows(const void* src, void* dst, int groups, int rows, int row_bytes, cudaStream_t s);
+cudaError_t launch_scale_layout(const int32_t* src, int32_t* dst, int groups, int rows, int row_stride, int kwords,
+                                int interleave, cudaStream_t s);
 int ep_sync_bytes();
 int ep_totals_offset();                      // byte offset of the [32][32] route-total table inside the ep_sync region
 cudaError_t launch_ep_signal_return(const Ctx& c, const void* const* peer_ws, int64_t timeout_ns, cudaStream_t s);
