@@ -216,8 +216,9 @@ def run_ours(args):
     step_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     value = world * m / (step_ms * 1e-3)
     # quantiser, 3 route-ordering passes, plan, place, GEMM1, GEMM2, combine; the peer exchange adds publish, push, the
-    # return copy (or, fused into GEMM2, its flag kernel) and 2 flag waits; the NCCL exchange adds the pack kernel
-    launches_per_step = 9 if world == 1 else (10 if args.ep_transport == "nccl" else 14)
+    # return copy and 2 flag waits (14); with the write-back fused into GEMM2 the copy becomes a flag kernel and the
+    # shared expert gets its own plan and two GEMM launches ahead of the routed ones (17); NCCL: the pack kernel (10)
+    launches_per_step = 9 if world == 1 else {"nccl": 10, "peer-unfused": 14, "peer": 17}[args.ep_transport]
 
     # ---- end to end through the public API with host buffers (pinned): every step copies its inputs host -> device and
     # its result device -> host inside the timed region.  The copies of step i+1 / i-1 run on a second stream while step
