@@ -126,6 +126,31 @@ def test_layout_is_consistent():
         _native.layout_of(_native.MmoeGeometry(1, 0, 384, 6, 5120, 2304, 2, 3840))
 
 
+def test_entry_points_reject_bad_arguments_before_touching_the_device():
+    """Argument errors come back as status codes from the C ABI (mapped to the reference's exception classes) without
+    any CUDA call, so they can be checked on a machine without a GPU."""
+    from vllm_plugin_b200.backend import _native
+    lib = _native.load()
+    buf = (ctypes.c_int32 * 64)()
+    p = ctypes.addressof(buf)
+    with pytest.raises(AssertionError, match="multiple of 128"):
+        _native.check(lib.mmoe_transform_weights(p, p + 64, p, p + 128, 1, 100, 64, 1, 1, None))
+    with pytest.raises(AssertionError, match="distinct"):
+        _native.check(lib.mmoe_transform_weights(None, None, p, p, 1, 128, 64, 1, 0, None))
+    geo1 = _native.MmoeGeometry(1, 0, 384, 6, 5120, 2304, 1, 3840)
+    opts = _native.MmoeOptions(10.0, 1, 0, 2000, 0)
+    w = _native.MmoeWeights()
+    peers = (ctypes.c_void_p * 1)(p)
+    with pytest.raises(AssertionError, match="num_ranks > 1"):
+        _native.check(lib.mmoe_forward_ep(ctypes.byref(geo1), p, peers, ctypes.byref(w), ctypes.byref(opts), p, 1, 16, None, None))
+    with pytest.raises(AssertionError, match="num_ranks > 1"):
+        _native.check(lib.mmoe_experts_ep_return(ctypes.byref(geo1), p, peers, ctypes.byref(w), ctypes.byref(opts), 1, 16, None))
+    geo2 = _native.MmoeGeometry(2, 0, 384, 6, 5120, 2304, 1, 3840)
+    peers2 = (ctypes.c_void_p * 2)(p, None)
+    with pytest.raises(AssertionError, match="NULL"):
+        _native.check(lib.mmoe_forward_ep(ctypes.byref(geo2), p, peers2, ctypes.byref(w), ctypes.byref(opts), p, 1, 16, None, None))
+
+
 def test_import_is_light():
     import subprocess
     import sys
