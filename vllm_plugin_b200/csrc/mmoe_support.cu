@@ -182,7 +182,6 @@ __device__ void warp_rank_routes(const int32_t* ids, int n, int32_t* count, int3
 }
 
 constexpr int kSortThreads = 256;
-constexpr int kMaxChunkRoutes = kSortChunkTokens * 32;
 
 // pass A: per chunk, local rank of every route among the chunk's routes to the same expert + per-chunk expert counts
 __global__ void __launch_bounds__(kSortThreads) sort_local_kernel(

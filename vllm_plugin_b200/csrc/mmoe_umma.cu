@@ -29,6 +29,14 @@ namespace mmoe {
 
 namespace {
 
+#ifndef MMOE_TRACE
+#define MMOE_TRACE 0
+#endif
+// Timing experiments (ablation mask, L2 prefetch distance) are compiled in only on request: their per-stage tests sit
+// in one-thread loops that run at instruction latency.
+#ifndef MMOE_EXPERIMENTS
+#define MMOE_EXPERIMENTS 0
+#endif
 constexpr int kThreads = 224;   // producer, MMA 0, 4 epilogue warps, MMA 1
 constexpr int kSmemBudget = 227 * 1024 - 2048;   // dynamic shared memory we ask for at most (alignment slack excluded)
 constexpr uint32_t kTmemCols = 512;
@@ -38,8 +46,6 @@ constexpr int kSpinProbes = 1;             // non-blocking probes before a wait 
 struct UmmaParams {
   CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 128 rows
   CUtensorMap map_w_shared;    // E4M3 weights of the shared expert
-  CUtensorMap map_tok_routed;  // E4M3 token rows (pool / activations), box 128 K x kBoxRows
-  CUtensorMap map_tok_shared;
   const char* plan;
   const int32_t* wsf_routed;   // [E_l][K/128][rows_per_expert] scale words, 4x32 transposed per 128 rows
   const int32_t* wsf_shared;
@@ -80,7 +86,9 @@ struct UmmaParams {
   int prefetch_ahead;          // K stages of weights requested from DRAM into L2 ahead of the pipeline (0 = off)
   int ablate;                  // timing experiments only (results become meaningless): bit 0 skip weight-scale copies,
                                // 1 token-scale copies, 2 token tiles, 3 tcgen05.cp, 4 MMAs, 5 weight tiles
-  CUtensorMap map_w_routed_packed;     // experiment only (ablate bit 7): the packed FP4 bytes as plain bytes
+#if MMOE_EXPERIMENTS
+  CUtensorMap map_w_routed_packed;     // ablate bit 7: the packed FP4 bytes as plain bytes
+#endif
   CUtensorMap map_tok_routed_box[5];   // token maps with boxes of 16 / 32 / 64 / 80 / 128 rows
   CUtensorMap map_tok_shared_box[5];
 };
@@ -202,31 +210,12 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled, 8-row groups 1024
-// bytes apart.  Bits: [0,14) address>>4, [16,30) leading byte offset>>4 (unused here), [32,46) stride byte offset>>4,
-// [46,48) version = 1, [61,64) layout (2 = 128-byte swizzle).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// Descriptor of a 512-byte scale chunk for tcgen05.cp: no swizzle, 8-row (128-byte) groups back to back.
-__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
-}
 // Instruction descriptor of the block-scaled MMA: [4,6) B scale id, [7,10) A format, [10,13) B format (0 = E4M3,
 // 5 = E2M1), [15]/[16] A/B major (0 = K), [17,23) N>>3, [23] scale format (1 = UE8M0), [24,29) M>>4, [29,31) A scale id.
 __device__ __forceinline__ uint32_t make_idesc(uint32_t a_format, uint32_t n, uint32_t sf_id) {
   return (sf_id << 4) | (a_format << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf_id << 29);
 }
 
-#ifndef MMOE_TRACE
-#define MMOE_TRACE 0
-#endif
-// Timing experiments (ablation mask, L2 prefetch distance) are compiled in only on request: their per-stage tests sit
-// in one-thread loops that run at instruction latency.
-#ifndef MMOE_EXPERIMENTS
-#define MMOE_EXPERIMENTS 0
-#endif
 #if MMOE_TRACE
 #define TR_DECL(n) long long n = 0
 #define TR_T0() long long tr_t0 = clock64()
@@ -402,8 +391,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int n16 = (tile.n_valid + 15) & ~15;
         const int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : (n16 <= 80 ? 3 : 4)));   // never above kBoxRows
         const uint32_t box_rows = box_sel == 3 ? 80u : (box_sel == 4 ? 128u : (16u << box_sel));
+#if MMOE_EXPERIMENTS
         const CUtensorMap* wmap = shared ? &p.map_w_shared : ((ab & 128) ? &p.map_w_routed_packed : &p.map_w_routed);
         const int kdiv = (!shared && (ab & 128)) ? 2 : 1;      // byte coordinates of the packed view
+#else
+        const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
+        constexpr int kdiv = 1;
+#endif
         const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
         const int e = shared ? 0 : tile.expert;
         // The 256 stored weight rows of the task.  Layer 1 reads W13 in its stored order [g0..7, u0..7, g8..15, ...]
@@ -856,17 +850,14 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   UmmaParams p1{};
   int bad = 0;
   bad |= make_w13_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
-  bad |= make_map(&p1.map_tok_routed, false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, box, false);
-  if (has_shared) {
-    bad |= make_w13_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
-    bad |= make_map(&p1.map_tok_shared, false, c.ws + c.lay.x, h, c.geo.num_max_tokens, box, false);
-  } else {
-    p1.map_w_shared = p1.map_w_routed;
-    p1.map_tok_shared = p1.map_tok_routed;
-  }
+  if (has_shared) bad |= make_w13_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
+  else p1.map_w_shared = p1.map_w_routed;
+#if MMOE_EXPERIMENTS
   bad |= make_packed_map(&p1.map_w_routed_packed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
+#endif
+  // token maps: one per box size a tile of this launch can pick (never above the kernel's own box)
   const uint32_t kBoxes[5] = {16, 32, 64, 80, 128};
-  for (int b = 0; b < 5; ++b) {
+  for (int b = 0; b < 5 && (int)kBoxes[b] <= box; ++b) {
     bad |= make_map(&p1.map_tok_routed_box[b], false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b], false);
     if (has_shared) bad |= make_map(&p1.map_tok_shared_box[b], false, c.ws + c.lay.x, h, c.geo.num_max_tokens, kBoxes[b], false);
     else p1.map_tok_shared_box[b] = p1.map_tok_routed_box[b];
@@ -904,16 +895,12 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
 
   UmmaParams p2 = p1;
   bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
-  bad |= make_map(&p2.map_tok_routed, false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, box, false);
-  if (has_shared) {
-    bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0);
-    bad |= make_map(&p2.map_tok_shared, false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, box, false);
-  } else {
-    p2.map_w_shared = p2.map_w_routed;
-    p2.map_tok_shared = p2.map_tok_routed;
-  }
+  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0);
+  else p2.map_w_shared = p2.map_w_routed;
+#if MMOE_EXPERIMENTS
   bad |= make_packed_map(&p2.map_w_routed_packed, false, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
-  for (int b = 0; b < 5; ++b) {
+#endif
+  for (int b = 0; b < 5 && (int)kBoxes[b] <= box; ++b) {
     bad |= make_map(&p2.map_tok_routed_box[b], false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b], false);
     if (has_shared) bad |= make_map(&p2.map_tok_shared_box[b], false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, kBoxes[b], false);
     else p2.map_tok_shared_box[b] = p2.map_tok_routed_box[b];
