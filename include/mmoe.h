@@ -213,8 +213,10 @@ int mmoe_transform_weights(const void* w_in, void* w_out, const int32_t* sf_in, 
 int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream);
 
 /* Process-wide tuning of the tensor-core kernels (the reference keeps such knobs in `KernelOptions`,
- * backend/frontend.py:72-116): `prefetch_ahead` = K stages of weight traffic requested into L2 ahead of the
- * shared-memory pipeline (< 0: built-in default, 0: off); `max_stages` = cap on the pipeline depth (0: no cap). */
+ * backend/frontend.py:72-116): `max_stages` = cap on the shared-memory pipeline depth (0: no cap).  `prefetch_ahead`
+ * (K stages of weight traffic requested into L2 ahead of the pipeline; < 0: built-in default, 0: off) is honoured only
+ * by libraries built with -DMMOE_EXPERIMENTS=1: measured on B200 it never helps, so the default build compiles the test
+ * out of the one-thread producer loop. */
 int mmoe_set_tuning(int32_t prefetch_ahead, int32_t max_stages);
 
 const char* mmoe_status_string(int code);
