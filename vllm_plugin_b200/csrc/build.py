@@ -41,6 +41,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
         cmd[1:1] = ["-Xptxas", "-v"]
     if os.environ.get("MMOE_EXPERIMENTS"):    # ablation mask and L2 prefetch distance honoured by the kernels (development only)
         cmd[1:1] = ["-DMMOE_EXPERIMENTS=1"]
+    if os.environ.get("MMOE_EP_TRACE"):       # phase times of the expert-parallel forward, printed per rank (development only)
+        cmd[1:1] = ["-DMMOE_EP_TRACE=1"]
     if os.environ.get("MMOE_TRACE"):          # per-role cycle counters printed by block 0 (development only)
         cmd[1:1] = ["-DMMOE_TRACE=1"]
     res = subprocess.run(cmd, capture_output=True, text=True)
