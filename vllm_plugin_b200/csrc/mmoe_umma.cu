@@ -20,6 +20,11 @@
 // buffered so the epilogue of task i overlaps the loads and MMAs of task i+1.  Every wait is bounded: when the budget
 // expires the CTA records {kernel, role, block} in the status words, lets its in-flight copies land, frees its TMEM and
 // returns; nothing traps.
+//
+// Expert parallelism: layer 2 has a second form (kFused) whose epilogue stores every BF16 row straight into the buffer
+// of the rank the token came from (plain peer stores over NVLink, no TMA from or to peer memory), and `tile_select`
+// restricts a launch to the routed tiles or to the shared expert's tiles planned ahead, so that the shared expert can
+// run while the dispatch is still in flight on another stream.
 #include <cuda.h>
 #include <stdio.h>
 
