@@ -175,6 +175,15 @@ int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_to
 /* Grouped GEMM1 -> SwiGLU/requant -> grouped GEMM2 for routed and shared experts. */
 int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  int32_t num_tokens, int32_t block_m, void* stream);
+/* The two halves of `mmoe_experts` that `mmoe_forward_ep` runs on either side of the join, exported for hosts that build
+ * their own overlap (and so that the split can be checked on one GPU): `mmoe_plan_shared` plans the shared expert's
+ * tiles from the token count alone (before any receive count is known); `mmoe_experts_select` runs both GEMMs over
+ * `tile_select` = 0 every tile of the plan (= `mmoe_experts`), 1 the routed tiles only, 2 the shared expert's tiles
+ * written by `mmoe_plan_shared`.  Selections 1 and 2 together leave exactly what selection 0 leaves.  Corresponds to
+ * the reference scheduling shared-expert blocks ahead of the routed ones (backend/kernel/scheduler.py:250-259). */
+int mmoe_plan_shared(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, int32_t block_m, void* stream);
+int mmoe_experts_select(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
+                        int32_t num_tokens, int32_t block_m, int32_t tile_select, void* stream);
 /* EP>1, device-side transport: `mmoe_experts` with the write-back fused into GEMM2 -- the epilogue stores every BF16
  * output row straight into the `ret_recv` of the rank its token came from (peer stores over NVLink while the tensor
  * cores work on the next tile), then barrier 2 is published and awaited.  Replaces `mmoe_experts` + `mmoe_ep_return`;

@@ -244,3 +244,39 @@ def test_cuda_graph_replay_of_every_variant():
         x.copy_(hid_b.cuda())
         g.replay()
         assert_parity(y, H.oracle_layer(layer, hid_b, ids, w), f"graph replay m={m}")
+
+
+@pytest.mark.parametrize("m,bm", [(7, 16), (130, 32), (300, 128), (300, 192)])
+def test_shared_expert_ahead_of_the_routed_plan(m, bm):
+    """The split the expert-parallel forward uses, on one GPU: shared expert planned and run first (both GEMMs), routed
+    experts afterwards, leaves bit for bit what one launch over the whole plan leaves."""
+    import ctypes
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend import _native
+    from vllm_plugin_b200.backend.frontend import _weights_struct, check_mega_moe_arguments, read_status
+    layer = H.make_layer(shared=True, seed=21, **SMALL)
+    hid = O.make_hidden(m, layer.hidden, 3)
+    ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 4, zipf_s=1.2, mask_frac=0.05)
+    api.set_kernel_options(block_m=bm)
+    try:
+        y_whole, buf = H.run_layer(layer, hid, ids, w)
+    finally:
+        api.set_kernel_options(block_m=0)
+    dev = torch.device("cuda", 0)
+    l1, l2, sl1, sl2 = H.kernel_weights(layer, dev)
+    y = torch.empty_like(y_whole)
+    s13, s2 = check_mega_moe_arguments(y, l1, l2, buf, sl1, sl2, None, (1, 1, 32), "swiglu", 10.0, True, 1.0, 0.0)
+    ws = _weights_struct(l1, l2, sl1, sl2, s13, s2)
+    lib = _native.load()
+    geo, base = ctypes.byref(buf.geo), buf.base_ptr
+    opts = _native.MmoeOptions(10.0, 1, 0, 2000, 0)
+    sp = torch.cuda.current_stream(dev).cuda_stream
+    api.stage_inputs_for_mega_moe(buf, hid.to(dev), ids.to(dev), w.to(dev), block_m=bm)
+    _native.check(lib.mmoe_plan_shared(geo, base, m, bm, sp))
+    _native.check(lib.mmoe_experts_select(geo, base, ctypes.byref(ws), ctypes.byref(opts), m, bm, 2, sp))
+    _native.check(lib.mmoe_dispatch_count(geo, base, m, sp))
+    _native.check(lib.mmoe_dispatch_place(geo, base, m, bm, None, sp))
+    _native.check(lib.mmoe_experts_select(geo, base, ctypes.byref(ws), ctypes.byref(opts), m, bm, 1, sp))
+    _native.check(lib.mmoe_combine(geo, base, y.data_ptr(), m, sp))
+    read_status(buf)
+    assert torch.equal(y, y_whole)

@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "mmoe_dispatch_place", "mmoe_experts", "mmoe_combine", "mmoe_forward", "mmoe_read_status", "mmoe_status_string",
     "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc", "mmoe_ep_dispatch", "mmoe_ep_return",
     "mmoe_experts_ep_return", "mmoe_forward_ep", "mmoe_transform_weights",
+    "mmoe_plan_shared", "mmoe_experts_select",
 )
 
 
@@ -101,6 +102,8 @@ def load() -> ctypes.CDLL:
     lib.mmoe_ep_return.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeOptions), vp]
     lib.mmoe_forward_ep.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeWeights), ctypes.POINTER(MmoeOptions),
                                     vp, i32, i32, vp, vp]
+    lib.mmoe_plan_shared.argtypes = [geo_p, vp, i32, i32, vp]
+    lib.mmoe_experts_select.argtypes = [geo_p, vp, ctypes.POINTER(MmoeWeights), ctypes.POINTER(MmoeOptions), i32, i32, i32, vp]
     lib.mmoe_transform_weights.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.mmoe_experts_ep_return.argtypes = [geo_p, vp, ctypes.POINTER(vp), ctypes.POINTER(MmoeWeights),
                                            ctypes.POINTER(MmoeOptions), i32, i32, vp]

@@ -372,6 +372,24 @@ int mmoe_experts(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
   return run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream);
 }
 
+int mmoe_plan_shared(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, int32_t block_m, void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc == MMOE_OK) rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
+  cudaError_t e = mmoe::launch_shared_plan(c, num_tokens, block_m, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "shared plan launch");
+}
+
+int mmoe_experts_select(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
+                        int32_t num_tokens, int32_t block_m, int32_t tile_select, void* stream) {
+  if (tile_select < 0 || tile_select > 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "tile_select=%d outside [0, 2]", tile_select);
+  if (opt != nullptr && opt->engine != 0 && tile_select != 0)
+    return fail(MMOE_ERR_UNSUPPORTED, "only the tensor-core engine can run a subset of the tiles");
+  return run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, tile_select);
+}
+
 int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void* const* peer_workspaces,
                            const MmoeWeights* weights, const MmoeOptions* opt, int32_t num_tokens, int32_t block_m,
                            void* stream) {
