@@ -215,10 +215,11 @@ def run_ours(args):
     barrier()
     step_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     value = world * m / (step_ms * 1e-3)
-    # quantiser, 3 route-ordering passes, plan, place, GEMM1, GEMM2, combine; the peer exchange adds publish, push, the
-    # return copy and 2 flag waits (14); with the write-back fused into GEMM2 the copy becomes a flag kernel and the
-    # shared expert gets its own plan and two GEMM launches ahead of the routed ones (17); NCCL: the pack kernel (10)
-    launches_per_step = 9 if world == 1 else {"nccl": 10, "peer-unfused": 14, "peer": 17}[args.ep_transport]
+    # EP1: quantiser, 3 route-ordering passes, plan, place, shared-expert plan, 2 shared-expert GEMMs (running beside
+    # the ordering / placement on a second stream), 2 routed GEMMs, combine = 12 (6 at M <= 128: one fused ordering/plan
+    # launch and one launch per GEMM).  The peer exchange adds publish, push, 2 flag waits and a flag kernel (17);
+    # its unfused form has one launch per GEMM and a return copy (14); NCCL: the pack kernel, one launch per GEMM (10)
+    launches_per_step = (12 if m > 128 else 6) if world == 1 else {"nccl": 10, "peer-unfused": 14, "peer": 17}[args.ep_transport]
 
     # ---- end to end through the public API with host buffers (pinned): every step copies its inputs host -> device and
     # its result device -> host inside the timed region.  The copies of step i+1 / i-1 run on a second stream while step

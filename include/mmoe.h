@@ -194,7 +194,9 @@ int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void*
                            void* stream);
 /* y[t] = bf16(sum of the token's valid slots in ascending order, shared expert last). */
 int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream);
-/* EP1 convenience: count, place, experts, combine. */
+/* EP1 convenience: count, place, experts, combine.  Past the decode sizes (num_tokens > 128, with a shared expert) the
+ * routed experts' ordering, plan and placement run on the library's second stream while the shared expert's GEMMs run
+ * on `stream` (fork / join with events, capturable); same result as the separate calls. */
 int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream);
 
