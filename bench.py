@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 H, I, E, K = 5120, 2304, 384, 6
 M_HEADLINE = 3840
 SWEEP = (1, 8, 64, 256, 1024, 2048, 3840)
-NCU_TRAFFIC_RATIO_GEMM1 = 1.056      # (dram__bytes_read + dram__bytes_write) / algorithmic bytes at E=64, M=640: profiles/umma_kernel_E64.md
+NCU_TRAFFIC_RATIO_GEMM1 = 1.049      # (dram__bytes_read + dram__bytes_write) / algorithmic bytes at E=64, M=640: profiles/umma_kernel_E64.md
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -307,7 +307,7 @@ def run_ours(args):
         ach = w13_bytes / (g1_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "umma_kernel<1> (grouped GEMM1 + SwiGLU/requant)", "achieved": ach,
                     "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": f"of {peak_kind}",
-                    # DRAM bytes per launch: ncu read+write of this kernel on the E=64 capture (profiles/) was 1.056x its
+                    # DRAM bytes per launch: ncu read+write of this kernel on the E=64 capture (profiles/) was 1.049x its
                     # algorithmic bytes; traffic grows with the experts hit, so the same ratio is applied here
                     "traffic": w13_bytes * NCU_TRAFFIC_RATIO_GEMM1, "traffic_source": "scaled from the E=64, M=640 ncu capture by the experts hit",
                     "algorithmic_bytes_per_launch": w13_bytes, "ms_per_launch": g1_ms}
