@@ -101,6 +101,11 @@ class ClockSampler:
 def cpu_reference(steps: int, warmup: int):
     from oracle import mmoe_oracle as O
     cores = os.cpu_count() or 1
+    try:
+        os.sched_setaffinity(0, range(cores))       # the CPU arm uses every host core, whatever the GPU arm was bound to
+    except OSError:
+        pass
+    cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
     e_sample, m_sample = 32, 128
     experts = O.make_experts(e_sample, H, I, seed=0)
@@ -144,6 +149,24 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------------------------
 # this backend
 # ---------------------------------------------------------------------------------------------------------------------
+def bind_to_gpu_cores(local_rank: int) -> None:
+    """Run this process on the CPU cores NVML reports as local to its GPU (best effort; a serving engine does the same
+    so that pinned staging buffers and the copy engines share a NUMA node)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = int(visible.split(",")[local_rank]) if visible and visible.split(",")[local_rank].isdigit() else local_rank
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cores = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1}
+        cores &= set(os.sched_getaffinity(0))
+        if cores:
+            os.sched_setaffinity(0, cores)
+    except Exception:
+        pass
+
+
 def run_ours(args):
     import ctypes
 
@@ -166,6 +189,7 @@ def run_ours(args):
     e_local = E // world
     t_cap = 3840
     sampler = ClockSampler(local_rank)      # NVML is initialised before anything is timed
+    bind_to_gpu_cores(local_rank)           # pinned host buffers are first touched on the GPU's own NUMA node
 
     syn = SyntheticLayer(H, I, e_local, True, dev, seed=0, first_expert=rank * e_local)
     buf = api.get_symm_buffer_for_mega_moe(group, E, t_cap, K, H, I, 1)
@@ -222,13 +246,14 @@ def run_ours(args):
     launches_per_step = (12 if m > 128 else 6) if world == 1 else {"nccl": 10, "peer-unfused": 14, "peer": 17}[args.ep_transport]
 
     # ---- end to end through the public API with host buffers (pinned): every step copies its inputs host -> device and
-    # its result device -> host inside the timed region.  The copies of step i+1 / i-1 run on a second stream while step
-    # i computes (two input and two output buffers), as a serving engine pipelines them.
+    # its result device -> host inside the timed region.  The copies of step i+1 / i-1 run on two copy streams (one per
+    # direction) while step i computes (two input and two output buffers), as a serving engine pipelines them.
     hid_h, ids_h, w_h = hid.cpu().pin_memory(), ids.cpu().pin_memory(), w.cpu().pin_memory()
     y_h = [torch.empty((m, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     ins = [(torch.empty_like(hid), torch.empty_like(ids), torch.empty_like(w)) for _ in range(2)]
     outs = [torch.empty((m, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    copy_stream = torch.cuda.Stream(dev)
+    copy_stream = torch.cuda.Stream(dev)       # host -> device
+    back_stream = torch.cuda.Stream(dev)       # device -> host: its own stream, the link is full duplex
     in_ready = [torch.cuda.Event() for _ in range(2)]
     in_free = [torch.cuda.Event() for _ in range(2)]
     out_ready = [torch.cuda.Event() for _ in range(2)]
@@ -255,11 +280,12 @@ def run_ours(args):
             layer_call(*ins[slot], outs[slot])
             in_free[slot].record(stream)
             out_ready[slot].record(stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(out_ready[slot])
+            with torch.cuda.stream(back_stream):
+                back_stream.wait_event(out_ready[slot])
                 y_h[slot].copy_(outs[slot], non_blocking=True)
-                out_free[slot].record(copy_stream)
+                out_free[slot].record(back_stream)
         stream.wait_stream(copy_stream)
+        stream.wait_stream(back_stream)
 
     e2e_run(3)
     barrier()
