@@ -2,6 +2,8 @@
 // sequencing of the kernels of one forward call.  Nothing here allocates device memory or synchronises.
 #include <math.h>
 #include <stdarg.h>
+
+#include <mutex>
 #include <stdio.h>
 #include <string.h>
 
@@ -42,9 +44,12 @@ struct SideLane {
 constexpr int kMaxDevices = 64;
 SideLane g_side[kMaxDevices];
 
+std::mutex g_side_mutex;
+
 SideLane* side_lane(bool may_create) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_side_mutex);
   SideLane& l = g_side[dev];
   if (l.stream == nullptr && may_create) {
     SideLane n;
@@ -519,6 +524,7 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   if (geo == nullptr || opt == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "geometry / options are NULL");
   if (geo->num_ranks < 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "mmoe_forward_ep is the num_ranks > 1 sequence");
   int rc = check_peers(geo, workspace, peer_workspaces);
+  if (rc == MMOE_OK && !valid_block_m(block_m)) rc = fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
   if (rc == MMOE_OK) rc = mmoe_dispatch_count(geo, workspace, num_tokens, stream);
   if (rc != MMOE_OK) return rc;
   cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
