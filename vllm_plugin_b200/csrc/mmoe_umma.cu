@@ -72,6 +72,7 @@ struct UmmaParams {
   // token came from (plain peer stores over NVLink), at that rank's send position
   int tile_select;             // 0: every tile of the plan, 1: routed tiles only, 2: the early shared tiles only
   int64_t early_shared_first;  // index of the first early shared tile in the tile table
+  int early_shared_cap;        // tile records reserved there
   int fused_return;
   int ep_me;
   const int32_t* ep_totals;    // [32][32]: totals[s][d] = routes rank s sent to rank d in this call
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
   PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
   const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
   const int num_tiles = p.tile_select == 2
-                            ? (p.has_shared_weights ? pv.hdr->num_early_shared_tiles : 0)
+                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
                             : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
   const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
   const int k_stages = p.k_dim / kTileK;
@@ -897,6 +898,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p1.has_shared_weights = has_shared ? 1 : 0;
   p1.tile_select = c.tile_select;
   p1.early_shared_first = c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens);
+  p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
 
   UmmaParams p2 = p1;
   bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
