@@ -43,7 +43,7 @@ namespace {
 #define MMOE_EXPERIMENTS 0
 #endif
 constexpr int kThreads = 224;   // producer, MMA 0, 4 epilogue warps, MMA 1
-constexpr int kSmemBudget = 227 * 1024 - 2048;   // dynamic shared memory we ask for at most (alignment slack excluded)
+constexpr int kSmemBudget = 227 * 1024 - 1024;   // the 227 KB a CTA may have, less the slack for aligning the base to 1024 bytes
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitHintNs = 200000;   // upper bound of one hardware-suspended barrier wait (the loop around it re-arms)
 constexpr int kSpinProbes = 1;             // non-blocking probes before a wait may suspend (more than one is slower)
@@ -309,6 +309,7 @@ struct Shape {
   static constexpr int kPrefetchAhead = 0;
   static_assert(kSfCol + 16 <= (int)kTmemCols, "TMEM budget");
   static_assert(kStages >= 3, "pipeline too shallow");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 // kFused (layer 2, EP > 1): every output row goes to the rank its token came from; compiled as kernels of its own so
