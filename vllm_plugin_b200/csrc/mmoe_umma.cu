@@ -296,10 +296,13 @@ struct Shape {
   static constexpr int kNCap = kBoxRows > kMaxTileTokens ? kMaxTileTokens : kBoxRows;   // accumulator columns per matrix (kBoxRows = largest tile)
   static constexpr int kABytes = 2 * kTileRows * kTileK;           // byte containers in shared memory
   static constexpr int kBBytes = kBoxRows * kTileK;
-  // scale area of a stage: [weight scales of the 256 stored rows, 1024][token scales 512].  Layer 2 receives the two
-  // 512-byte chunks in tensor-memory order; layer 1 receives them in stored (gate/up interleaved) order and the MMA
-  // warps rearrange them in place.
-  static constexpr int kSfBytes = 3 * 512;
+  // scale area of a stage: [weight scales of the two tiles, 2 x 512][token scales 512][layer 1: stored-order scales
+  // 1024].  Layer 2 receives the two 512-byte chunks in tensor-memory order.  Layer 1 receives them in stored (gate/up
+  // interleaved) order and the MMA warps rearrange them: into the first 1024 bytes from a separate landing area, or --
+  // for the 32-token variant, where the saved KB is a sixth pipeline stage -- in place (measured: in place costs the
+  // 4-stage 128-row variant 5 % of its GEMM1 time and buys the others nothing).
+  static constexpr bool kSfInPlace = kLayer == 1 && kBoxRows == 32;
+  static constexpr int kSfBytes = 3 * 512 + (kLayer == 1 && !kSfInPlace ? 1024 : 0);
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
@@ -449,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
             }
           }
           // layer 1: raw scales of the 256 stored rows, permuted by warp 6; layer 2: two chunks already in order
-          if (!(ab & 1)) bulk_load(sf_dst, wsf, 1024, bar);
+          if (!(ab & 1)) bulk_load(sf_dst + (kLayer == 1 && !S::kSfInPlace ? 3 * 512 : 0), wsf, 1024, bar);
           if (!(ab & 4)) tma_load_2d(b0 + stage * S::kBBytes, tmap, k0, tile.row0, bar);
           if (!(ab & 2)) bulk_load(sf_dst + 2 * 512, tsf, 512, bar);
           if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -481,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       const uint64_t sw128_hi = (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
       const uint64_t sf_hi = (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
       // layer 1: the four 8-row groups of a weight tile's scales sit 256 bytes apart (see the rearrangement below)
-      const uint64_t sfa_hi = kLayer == 1 ? ((static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 46)) : sf_hi;
+      const uint64_t sfa_hi = S::kSfInPlace ? ((static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 46)) : sf_hi;
       const uint32_t a_lo0 = ((smem_u32(a_base) & 0x3FFFFu) >> 4) + h * (kTileRows * kTileK >> 4);
       const uint32_t b_lo0 = (smem_u32(b_base) & 0x3FFFFu) >> 4;
       const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
@@ -519,12 +522,22 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
           const uint32_t a_lo = a_lo0 + stage * (S::kABytes >> 4);
           const uint32_t b_lo = b_lo0 + stage * (S::kBBytes >> 4);
           const uint32_t sf_lo = sf_lo0 + stage * (S::kSfBytes >> 4);
-          if (kLayer == 1) {
-            // In place.  In stored order the scale words of the gate rows (h = 0) occupy words [64b, 64b + 32) of the
-            // 256-word area (b = 0..3) and those of the up rows (h = 1) words [64b + 32, 64b + 64): the 128 words a
-            // warp reads are exactly the 128 it may overwrite, so the two warps never touch each other's words.  The
-            // rearranged tile is four 128-byte groups of 8 rows, 256 bytes apart, which is what the copy descriptor
-            // below describes.
+          if (kLayer == 1 && !S::kSfInPlace) {
+            uint32_t* out = reinterpret_cast<uint32_t*>(sf_base + stage * S::kSfBytes) + 128 * h;
+            const uint32_t* in = reinterpret_cast<const uint32_t*>(sf_base + stage * S::kSfBytes) + 3 * 128;
+            uint32_t v[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) v[t] = in[src[t]];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) out[lane + 32 * t] = v[t];
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to tcgen05.cp
+            __syncwarp();
+          }
+          if (S::kSfInPlace) {
+            // In stored order the scale words of the gate rows (h = 0) occupy words [64b, 64b + 32) of the 256-word
+            // area (b = 0..3) and those of the up rows (h = 1) words [64b + 32, 64b + 64): the 128 words a warp reads
+            // are exactly the 128 it may overwrite, so the two warps never touch each other's words.  The rearranged
+            // tile is four 128-byte groups of 8 rows, 256 bytes apart, which is what the copy descriptor describes.
             uint32_t* area = reinterpret_cast<uint32_t*>(sf_base + stage * S::kSfBytes);
             uint32_t v[4];
 #pragma unroll
@@ -532,12 +545,12 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
             __syncwarp();                                                  // every lane has read before any lane writes
 #pragma unroll
             for (int t = 0; t < 4; ++t) area[64 * t + 32 * h + lane] = v[t];
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to tcgen05.cp
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
           }
           if (elect_one()) {
             if (!(ab & 8)) {
-              tc_cp_sf(sfa_col, sfa_hi | (sf_lo + (kLayer == 1 ? 8 : 32) * h));
+              tc_cp_sf(sfa_col, sfa_hi | (sf_lo + (S::kSfInPlace ? 8 : 32) * h));
               tc_cp_sf(sfb_col, sf_hi | (sf_lo + 64));
             }
             if (!(ab & 16)) {
