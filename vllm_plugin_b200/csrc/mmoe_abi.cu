@@ -597,6 +597,8 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   return rc;
 }
 
+#undef EP_TR
+
 int mmoe_transform_weights(const void* w_in, void* w_out, const int32_t* sf_in, int32_t* sf_out, int32_t num_groups,
                            int32_t rows, int32_t k_packed_bytes, int32_t k_words, int32_t interleave, void* stream) {
   if (num_groups <= 0 || rows <= 0 || k_packed_bytes <= 0 || k_words <= 0)
