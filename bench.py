@@ -195,7 +195,7 @@ def run_ours(args):
     buf = api.get_symm_buffer_for_mega_moe(group, E, t_cap, K, H, I, 1)
     api.precompile_mega_moe_variants(world, E, t_cap, K, H, I, 1, activation_clamp=10.0)
     api.set_kernel_options(ep_transport="nccl" if args.ep_transport == "nccl" else "peer",
-                           fuse_return=args.ep_transport == "peer")
+                           fuse_return=args.ep_transport == "peer", orientation=args.orientation)
     lib = _native.load()
     stats = torch.zeros(e_local, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev)
@@ -449,6 +449,8 @@ def main():
     ap.add_argument("--ep-transport", default="peer", choices=("peer", "peer-unfused", "nccl"),
                     help="N > 1: device-side NVLink exchange with the write-back fused into GEMM2 (default), the same "
                          "with a separate copy kernel, or the host-driven NCCL all-to-allv")
+    ap.add_argument("--orientation", type=int, default=0, choices=(0, 1, 2),
+                    help="grouped-GEMM kernel family: 0 chosen per call, 1 weights-as-A, 2 tokens-as-A")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -89,10 +89,12 @@ int mmoe_layout(const MmoeGeometry* geo, MmoeLayout* out);
 int mmoe_block_m(int32_t num_ranks, int32_t num_experts, int32_t num_tokens, int32_t num_topk);
 
 /* Load the kernels of every BLOCK_M variant, raise their dynamic shared-memory limits and resolve the driver entry
- * points used for tensor maps.  Must run once per process and device before any launch and outside stream capture.
- * Replaces `precompile_mega_moe_variants` (api.py:179-206; backend/frontend.py:851-897) and the JIT cache
- * (backend/jit.py:350-395).  `block_ms` receives the prepared variants (capacity `cap`), `*n` their number. */
-int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_t* n);
+ * points used for tensor maps.  Must run once per device (with that device current) before any launch there, and
+ * outside stream capture: `stream` is the stream the caller will launch on, and the call is refused with
+ * MMOE_ERR_NOT_PREPARED while it is capturing.  Replaces `precompile_mega_moe_variants` (api.py:179-206;
+ * backend/frontend.py:851-897) and the JIT cache (backend/jit.py:350-395).  `block_ms` receives the prepared variants
+ * (capacity `cap`), `*n` their number. */
+int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_t* n, void* stream);
 
 /* Kernel (a): BF16 hidden states -> MXFP8 E4M3 + packed UE8M0 scales, routing repack (padding -> id -1 / weight 0) and
  * the shared-expert scale scatter, written into the workspace views.  Replaces `prepare_megamoe_inputs`
@@ -219,16 +221,20 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
 int mmoe_transform_weights(const void* w_in, void* w_out, const int32_t* sf_in, int32_t* sf_out, int32_t num_groups,
                            int32_t rows, int32_t k_packed_bytes, int32_t k_words, int32_t interleave, void* stream);
 
-/* Copy the device status words to the host (synchronises the stream) and translate them: MMOE_OK or
- * MMOE_ERR_DEVICE_TIMEOUT.  Replaces the reference's device `trap` after a 300 s spin (backend/kernel/comm.py:229-250). */
+/* Copy the device status words to the host (synchronises the stream), clear them on the device and translate them:
+ * MMOE_OK, MMOE_ERR_DEVICE_TIMEOUT (a bounded wait expired: the outputs of that call are not valid) or
+ * MMOE_ERR_INVALID_ARGUMENT (expert ids >= num_experts were seen and treated as masked).  The words are sticky until
+ * read, so one read after any number of calls reports whether any of them failed; after the read a healthy call
+ * reports MMOE_OK again.  Replaces the reference's device `trap` after a 300 s spin (backend/kernel/comm.py:229-250). */
 int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, void* stream);
 
 /* Process-wide tuning of the tensor-core kernels (the reference keeps such knobs in `KernelOptions`,
- * backend/frontend.py:72-116): `max_stages` = cap on the shared-memory pipeline depth (0: no cap).  `prefetch_ahead`
- * (K stages of weight traffic requested into L2 ahead of the pipeline; < 0: built-in default, 0: off) is honoured only
- * by libraries built with -DMMOE_EXPERIMENTS=1: measured on B200 it never helps, so the default build compiles the test
- * out of the one-thread producer loop. */
-int mmoe_set_tuning(int32_t prefetch_ahead, int32_t max_stages);
+ * backend/frontend.py:72-116).  `max_stages`: cap on the shared-memory pipeline depth of the weights-as-A kernels (0: no
+ * cap).  `orientation`: 0 = chosen per call (tokens-as-A kernels from about 80 expected rows per expert, and for the
+ * shared expert of any call with more than 128 tokens; weights-as-A kernels below), 1 = weights-as-A always, 2 =
+ * tokens-as-A wherever the geometry allows (intermediate >= 192, hidden >= 384).  Every rank and every step of a call
+ * (planning, GEMM launches) must see the same setting. */
+int mmoe_set_tuning(int32_t max_stages, int32_t orientation);
 
 const char* mmoe_status_string(int code);
 const char* mmoe_last_error(void);   /* detail of the last failure on this thread */

@@ -66,7 +66,7 @@ def _to_device_keep_strides(t: torch.Tensor, device) -> torch.Tensor:
 
 
 def run_layer(layer: Layer, hidden, ids, w, *, t_max: int = 1920, clamp=10.0, fast_math=True, engine=0, pad=None,
-              localized=False, stats=None, buf=None, weights=None):
+              localized=False, stats=None, buf=None, weights=None, orientation=0):
     """Stage + forward on cuda:0 at EP1; returns ``(y, buf)``."""
     from vllm_plugin_b200 import api
     from vllm_plugin_b200.backend.workspace import SingleRankGroup
@@ -78,7 +78,7 @@ def run_layer(layer: Layer, hidden, ids, w, *, t_max: int = 1920, clamp=10.0, fa
     if weights is None:
         weights = kernel_weights(layer, dev, localized=localized)
     l1, l2, sl1, sl2 = weights
-    api.set_kernel_options(engine=engine)
+    api.set_kernel_options(engine=engine, orientation=orientation)
     try:
         m = hidden.shape[0]
         y = torch.empty((m, layer.hidden), dtype=torch.bfloat16, device=dev)
@@ -89,7 +89,7 @@ def run_layer(layer: Layer, hidden, ids, w, *, t_max: int = 1920, clamp=10.0, fa
         from vllm_plugin_b200.backend.frontend import read_status
         read_status(buf)
     finally:
-        api.set_kernel_options(engine=0)
+        api.set_kernel_options(engine=0, orientation=0)
     return y, buf
 
 

@@ -83,7 +83,7 @@ def load() -> ctypes.CDLL:
     geo_p = ctypes.POINTER(MmoeGeometry)
     lib.mmoe_layout.argtypes = [geo_p, ctypes.POINTER(MmoeLayout)]
     lib.mmoe_block_m.argtypes = [i32, i32, i32, i32]
-    lib.mmoe_prepare.argtypes = [geo_p, ctypes.POINTER(i32), i32, ctypes.POINTER(i32)]
+    lib.mmoe_prepare.argtypes = [geo_p, ctypes.POINTER(i32), i32, ctypes.POINTER(i32), vp]
     lib.mmoe_stage_inputs.argtypes = [geo_p, vp, vp, vp, i32, vp, vp, i32, i32, vp]
     lib.mmoe_dispatch_count.argtypes = [geo_p, vp, i32, vp]
     lib.mmoe_dispatch_pack.argtypes = [geo_p, vp, i32, vp]

@@ -34,6 +34,9 @@ class KernelOptions:
     fuse_return: bool = True    # "peer" transport: GEMM2's epilogue stores its rows straight into the source rank's
                                 # buffer over NVLink, and the dispatch overlaps the shared expert's GEMMs on a second
                                 # stream; False = one stream, separate copy kernel after GEMM2 (same result)
+    orientation: int = 0        # grouped-GEMM kernel family: 0 = chosen per call from the expected rows per expert,
+                                # 1 = weights-as-A (small token counts) always, 2 = tokens-as-A wherever the geometry
+                                # allows; every rank of a group must use the same value
 
 
 _kernel_options = KernelOptions()
@@ -45,6 +48,8 @@ def set_kernel_options(**kwargs: Any) -> KernelOptions:
     _kernel_options = dataclasses.replace(_kernel_options, **kwargs)
     if _kernel_options.block_m and _kernel_options.block_m not in _h.VALID_BLOCK_MS:
         raise AssertionError(f"block_m={_kernel_options.block_m} is not one of {_h.VALID_BLOCK_MS}")
+    if "orientation" in kwargs:
+        _native.check(_native.load().mmoe_set_tuning(0, int(_kernel_options.orientation)))
     return _kernel_options
 
 
@@ -91,7 +96,8 @@ def precompile_mega_moe_variants(num_ranks: int, num_experts: int, num_max_token
     geo = _native.MmoeGeometry(num_ranks, 0, num_experts, num_topk, hidden, intermediate_hidden, num_shared_experts, t)
     out = (ctypes.c_int32 * 8)()
     n = ctypes.c_int32(0)
-    _native.check(_native.load().mmoe_prepare(ctypes.byref(geo), out, 8, ctypes.byref(n)))
+    _native.check(_native.load().mmoe_prepare(ctypes.byref(geo), out, 8, ctypes.byref(n),
+                                              torch.cuda.current_stream().cuda_stream))
     variants = tuple(int(out[i]) for i in range(n.value))
     assert variants == _h.get_block_m_variants(num_ranks, num_experts, num_topk, t), "host and library disagree on the variants"
     _prepared[key] = variants

@@ -13,7 +13,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(os.path.dirname(HERE), "_lib")
-SOURCES = ("mmoe_abi.cu", "mmoe_support.cu", "mmoe_umma.cu", "mmoe_ep.cu", "mmoe_weights.cu")
+SOURCES = ("mmoe_abi.cu", "mmoe_support.cu", "mmoe_umma.cu", "mmoe_umma_tm.cu", "mmoe_ep.cu", "mmoe_weights.cu")
 LIB_NAME = "libmmoe_b200.so"
 
 
@@ -39,12 +39,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
            "-shared", "-o", lib_path()] + [os.path.join(HERE, s) for s in SOURCES]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
-    if os.environ.get("MMOE_EXPERIMENTS"):    # ablation mask and L2 prefetch distance honoured by the kernels (development only)
-        cmd[1:1] = ["-DMMOE_EXPERIMENTS=1"]
     if os.environ.get("MMOE_EP_TRACE"):       # phase times of the expert-parallel forward, printed per rank (development only)
         cmd[1:1] = ["-DMMOE_EP_TRACE=1"]
-    if os.environ.get("MMOE_TRACE"):          # per-role cycle counters printed by block 0 (development only)
-        cmd[1:1] = ["-DMMOE_TRACE=1"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

@@ -34,7 +34,6 @@ int cuda_fail(cudaError_t e, const char* what) {
 #endif
 
 const int kBlockMs[6] = {16, 32, 64, 128, 192, 240};
-bool g_prepared = false;
 
 // A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.
 struct SideLane {
@@ -101,6 +100,22 @@ int make_ctx(const MmoeGeometry* g, void* ws, mmoe::Ctx* c) {
   return MMOE_OK;
 }
 
+// Which kernel family runs a tile list, hence how the list is cut (tiles of up to 128 rows for the tokens-as-A
+// kernels).  A pure function of the call's geometry, token count and BLOCK_M, so that the planning step and the GEMM
+// launches of one call agree without talking to each other.  `early_shared`: the shared expert's tiles planned ahead
+// of the routed ones (tile_select 2); otherwise the routed tiles and the shared tiles planned with them.
+bool choose_token_major(const MmoeGeometry* g, int m, int block_m, bool early_shared) {
+  const bool fits = g->intermediate >= 192 && g->hidden / 2 >= 192;      // a half of each weight matrix holds a 192-row box
+  const int forced = mmoe::tuned_orientation();
+  if (!fits || forced == 1) return false;
+  if (forced == 2) return true;
+  if (early_shared) return m > 128;
+  // expected rows per expert (the quantity BLOCK_M is chosen from): below ~80 the weights-as-A kernels, whose cost
+  // follows the token count, win; above it the tensor-bound tokens-as-A form does
+  const double expected = (double)m * g->num_ranks * g->num_topk / g->num_experts;
+  return block_m >= 64 && expected >= 80.0;
+}
+
 int check_tokens(const MmoeGeometry* g, int m) {
   if (m < 0 || m > g->num_max_tokens) return fail(MMOE_ERR_INVALID_ARGUMENT, "num_tokens=%d outside [0, %d]", m, g->num_max_tokens);
   return MMOE_OK;
@@ -119,11 +134,12 @@ float bf16_round_host(float v) {
 
 extern "C" {
 
-int mmoe_abi_version(void) { return 1; }
+int mmoe_abi_version(void) { return 2; }
 
-int mmoe_set_tuning(int32_t prefetch_ahead, int32_t max_stages) {
-  if (max_stages < 0 || ((max_stages & 0xFFFF) > 0 && (max_stages & 0xFFFF) < 2)) return fail(MMOE_ERR_INVALID_ARGUMENT, "max_stages=%d must be 0 or >= 2", max_stages);
-  mmoe::set_tuning(prefetch_ahead, max_stages);
+int mmoe_set_tuning(int32_t max_stages, int32_t orientation) {
+  if (max_stages < 0 || max_stages == 1) return fail(MMOE_ERR_INVALID_ARGUMENT, "max_stages=%d must be 0 or >= 2", max_stages);
+  if (orientation < 0 || orientation > 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "orientation=%d outside [0, 2]", orientation);
+  mmoe::set_tuning(max_stages, orientation);
   return MMOE_OK;
 }
 
@@ -231,7 +247,7 @@ int mmoe_layout(const MmoeGeometry* g, MmoeLayout* out) {
   return MMOE_OK;
 }
 
-int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_t* n) {
+int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_t* n, void* stream) {
   int rc = check_geometry(geo);
   if (rc != MMOE_OK) return rc;
   int dev = 0;
@@ -242,11 +258,10 @@ int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_
   cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
   if (major != 10 || minor != 0) return fail(MMOE_ERR_ARCH, "compute capability %d.%d, need 10.0", major, minor);
   cudaStreamCaptureStatus cap_status = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(cudaStreamPerThread, &cap_status) == cudaSuccess && cap_status != cudaStreamCaptureStatusNone)
-    return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() called during stream capture");
+  if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cap_status) != cudaSuccess || cap_status != cudaStreamCaptureStatusNone)
+    return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() called while the stream is capturing");
   rc = mmoe::prepare_umma(*geo);
   if (rc != MMOE_OK) return fail(rc, "loading the tensor-core kernels failed: %s", cudaGetErrorString(cudaGetLastError()));
-  g_prepared = true;
   side_lane(true);                              // streams and events cannot be created while a stream is capturing
   // every BLOCK_M the geometry can select for M in [0, T]
   bool seen[6] = {false, false, false, false, false, false};
@@ -361,6 +376,7 @@ int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_to
   rc = check_tokens(geo, num_tokens);
   if (rc != MMOE_OK) return rc;
   if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
+  c.token_major = choose_token_major(geo, num_tokens, block_m, false);
   cudaError_t e = mmoe::launch_plan_place(c, num_tokens, block_m, stats, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_place launch");
 }
@@ -383,6 +399,7 @@ int mmoe_plan_shared(const MmoeGeometry* geo, void* workspace, int32_t num_token
   if (rc == MMOE_OK) rc = check_tokens(geo, num_tokens);
   if (rc != MMOE_OK) return rc;
   if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
+  c.token_major = choose_token_major(geo, num_tokens, block_m, true);
   cudaError_t e = mmoe::launch_shared_plan(c, num_tokens, block_m, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "shared plan launch");
 }
@@ -441,9 +458,10 @@ int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* pee
     e = mmoe::launch_experts_simt(c, *weights, o, num_tokens, block_m, st);
     if (e == cudaSuccess && peers != nullptr) e = mmoe::launch_ep_return(c, peers, timeout_ns, st);
   } else if (o.engine == 0) {
-    if (!g_prepared) return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() must run before the first launch");
+    if (!mmoe::tc_ready()) return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() must run on this device before the first launch");
     c.peer_ws = peers;
     c.tile_select = tile_select;
+    c.token_major = choose_token_major(geo, num_tokens, block_m, tile_select == 2);
     e = mmoe::launch_experts_umma(c, *weights, o, num_tokens, block_m, st);
     if (e == cudaSuccess && peers != nullptr) e = mmoe::launch_ep_signal_return(c, peers, timeout_ns, st);
   } else {
@@ -477,6 +495,7 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
       mmoe::Ctx c;
       int r = make_ctx(geo, workspace, &c);
       if (r != MMOE_OK) return r;
+      c.token_major = choose_token_major(geo, num_tokens, block_m, false);
       cudaError_t e = mmoe::launch_route_plan_place_small(c, num_tokens, block_m, stats, static_cast<cudaStream_t>(st));
       return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "route/plan launch");
     }
@@ -560,6 +579,7 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   // ... while the shared expert, which needs only this rank's own tokens, runs both of its GEMMs here
   mmoe::Ctx c;
   rc = make_ctx(geo, workspace, &c);
+  if (rc == MMOE_OK) c.token_major = choose_token_major(geo, num_tokens, block_m, true);
   if (rc == MMOE_OK && mmoe::launch_shared_plan(c, num_tokens, block_m, main_stream) != cudaSuccess)
     rc = cuda_fail(cudaGetLastError(), "shared plan launch");
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 2);
@@ -625,6 +645,8 @@ int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, 
   if (rc != MMOE_OK) return rc;
   int32_t host[8];
   cudaError_t e = cudaMemcpyAsync(host, c.ws + c.lay.status, sizeof host, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  // clear on read: the words are sticky on the device, so that a later healthy call is reported as healthy
+  if (e == cudaSuccess) e = cudaMemsetAsync(c.ws + c.lay.status, 0, sizeof host, static_cast<cudaStream_t>(stream));
   if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "reading the status words");
   if (words8 != nullptr) memcpy(words8, host, sizeof host);

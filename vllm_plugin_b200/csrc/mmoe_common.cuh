@@ -20,6 +20,9 @@ constexpr int kMaxTileTokens = 112;  // largest UMMA N of one task
 // tiles at 80 rows: the 10 KB token slot buys a fifth pipeline stage.  192 / 240 keep 112 (the tensor-bound
 // expert-parallel shapes, where fewer and larger tiles matter more than pipeline depth).
 __host__ __device__ inline int max_tile_rows(int block_m) { return block_m <= 64 ? block_m : (block_m == 128 ? 80 : kMaxTileTokens); }
+// Tile cap of a launch: the tokens-as-A kernels take tiles of up to 128 rows whatever BLOCK_M is.
+constexpr int kTokenMajorTileRows = 128;
+__host__ __device__ inline int tile_cap(int block_m, bool token_major) { return token_major ? kTokenMajorTileRows : max_tile_rows(block_m); }
 // Scale-factor chunks (128 token rows each) reserved per pool block of a BLOCK_M variant: at least as many as the
 // tiles an expert's rows are cut into (ceil(n / max_tile_rows) <= ceil(n / block_m) * chunks_per_block for every n).
 __host__ __device__ inline int chunks_per_block(int block_m) { return block_m <= 64 ? 1 : (block_m <= 192 ? 2 : 3); }
@@ -173,6 +176,7 @@ struct Ctx {             // resolved pointers of one call
   int kmax;              // min(k, E/R)
   const void* const* peer_ws = nullptr;   // set by the call that fuses the write-back into GEMM2 (EP > 1)
   int tile_select = 0;                    // 0: every tile of the plan, 1: routed tiles only, 2: the early shared tiles only
+  bool token_major = false;               // the tiles this call plans / runs are those of the tokens-as-A kernels (<= 128 rows)
   template <typename T> T* at(int64_t off) const { return reinterpret_cast<T*>(ws + off); }
 };
 
@@ -187,7 +191,9 @@ cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s);
 cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 int prepare_umma(const MmoeGeometry& geo);   // returns an MMOE_* code
-void set_tuning(int prefetch_ahead, int max_stages);
+bool tc_ready();                             // prepare_umma() has run on the current device
+void set_tuning(int max_stages, int orientation);
+int tuned_orientation();                     // 0: per call, 1: weights-as-A always, 2: tokens-as-A wherever the geometry allows
 cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_experts, int32_t* send_count,
                                int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route, cudaStream_t s);
 int route_order_static_max_tokens();

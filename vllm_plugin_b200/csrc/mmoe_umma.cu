@@ -25,31 +25,16 @@
 // of the rank the token came from (plain peer stores over NVLink, no TMA from or to peer memory), and `tile_select`
 // restricts a launch to the routed tiles or to the shared expert's tiles planned ahead, so that the shared expert can
 // run while the dispatch is still in flight on another stream.
-#include <cuda.h>
-#include <stdio.h>
-
-#include "mmoe_common.cuh"
+#include "mmoe_tc.cuh"
 
 namespace mmoe {
 
 namespace {
 
-#ifndef MMOE_TRACE
-#define MMOE_TRACE 0
-#endif
-// Timing experiments (ablation mask, L2 prefetch distance) are compiled in only on request: their per-stage tests sit
-// in one-thread loops that run at instruction latency.
-#ifndef MMOE_EXPERIMENTS
-#define MMOE_EXPERIMENTS 0
-#endif
 constexpr int kThreads = 224;   // producer, MMA 0, 4 epilogue warps, MMA 1
-constexpr int kSmemBudget = 227 * 1024 - 1024;   // the 227 KB a CTA may have, less the slack for aligning the base to 1024 bytes
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kWaitHintNs = 200000;   // upper bound of one hardware-suspended barrier wait (the loop around it re-arms)
-constexpr int kSpinProbes = 1;             // non-blocking probes before a wait may suspend (more than one is slower)
 
 struct UmmaParams {
-  CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 128 rows
+  CUtensorMap map_w_routed;    // FP4 weights, box 128 K x 256 rows (layer 1: the 5-D de-interleaving form)
   CUtensorMap map_w_shared;    // E4M3 weights of the shared expert
   const char* plan;
   const int32_t* wsf_routed;   // [E_l][K/128][rows_per_expert] scale words, 4x32 transposed per 128 rows
@@ -89,148 +74,9 @@ struct UmmaParams {
   int fast_math;
   int has_shared_weights;
   int num_stages;              // shared-memory pipeline depth in use (<= the compiled capacity)
-  int prefetch_ahead;          // K stages of weights requested from DRAM into L2 ahead of the pipeline (0 = off)
-  int ablate;                  // timing experiments only (results become meaningless): bit 0 skip weight-scale copies,
-                               // 1 token-scale copies, 2 token tiles, 3 tcgen05.cp, 4 MMAs, 5 weight tiles
-#if MMOE_EXPERIMENTS
-  CUtensorMap map_w_routed_packed;     // ablate bit 7: the packed FP4 bytes as plain bytes
-#endif
   CUtensorMap map_tok_routed_box[5];   // token maps with boxes of 16 / 32 / 64 / 80 / 128 rows
   CUtensorMap map_tok_shared_box[5];
 };
-
-// ---------------------------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ uint64_t global_timer() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kWaitHintNs)     // the thread sleeps in hardware until the phase completes or the hint expires
-      : "memory");
-  return ok != 0;
-}
-
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4) {
-  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global [%0, {%1, %2, %3, %4, %5}];"
-               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-// true in exactly one lane of the (converged) warp
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
-                                       uint32_t sfb, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Instruction descriptor of the block-scaled MMA: [4,6) B scale id, [7,10) A format, [10,13) B format (0 = E4M3,
-// 5 = E2M1), [15]/[16] A/B major (0 = K), [17,23) N>>3, [23] scale format (1 = UE8M0), [24,29) M>>4, [29,31) A scale id.
-__device__ __forceinline__ uint32_t make_idesc(uint32_t a_format, uint32_t n, uint32_t sf_id) {
-  return (sf_id << 4) | (a_format << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf_id << 29);
-}
-
-#if MMOE_TRACE
-#define TR_DECL(n) long long n = 0
-#define TR_T0() long long tr_t0 = clock64()
-#define TR_ADD(n) do { long long tr_t1 = clock64(); n += tr_t1 - tr_t0; tr_t0 = tr_t1; } while (0)
-#else
-#define TR_DECL(n)
-#define TR_T0()
-#define TR_ADD(n)
-#endif
 
 struct Control {          // lives at the start of shared memory
   uint64_t full[16];      // producer -> MMA warps: the stage's copies have landed
@@ -246,46 +92,6 @@ struct Control {          // lives at the start of shared memory
   int32_t home_base[32];  // ... and the send position on that rank of the first row it sent here
 };
 static_assert(sizeof(Control) <= 1024, "control block");
-constexpr uint32_t kOutSlotShift = 26;   // packed destination: slot << 26 | row
-
-struct Waiter {
-  Control* ctl;
-  int32_t* status;
-  uint64_t deadline;
-  int kernel_id, role;
-  // whole-warp wait: one lane watches the barrier, the others sleep at the warp barrier (a polling warp would put 32
-  // requests on the barrier unit per probe and slow the producer and MMA threads that share it)
-  __device__ __forceinline__ bool wait_warp(uint32_t bar, uint32_t parity) {
-    // common case: the phase has completed already -- one probe by the whole warp (one broadcast read) and a vote
-    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
-    bool ok = true;
-    if ((threadIdx.x & 31) == 0) ok = wait(bar, parity);
-    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-  }
-  // true when the phase completed, false when the call is being abandoned
-  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
-    // short non-blocking spin first: a hardware-suspended wait wakes up late, and that latency lands on the critical
-    // path of whichever role the pipeline is waiting for
-#pragma unroll 1
-    for (int i = 0; i < kSpinProbes; ++i)
-      if (mbar_test_wait(bar, parity)) return true;
-    for (uint32_t spin = 0;; ++spin) {
-      if (mbar_try_wait(bar, parity)) return true;
-      if ((spin & 63u) == 63u) {
-        if (ctl->abort_flag != 0) return false;
-        if (global_timer() > deadline) {
-          ctl->abort_flag = 1;
-          if (atomicCAS(&status[kStatusTimeout], 0, 1) == 0) {
-            status[kStatusKernel] = kernel_id;
-            status[kStatusRole] = role;
-            status[kStatusBlock] = static_cast<int32_t>(blockIdx.x);
-          }
-          return false;
-        }
-      }
-    }
-  }
-};
 
 // Every task multiplies TWO 128-row weight tiles with one token tile: layer 1 the gate rows and the up rows of 128
 // channels, layer 2 two consecutive 128-row blocks of W2.  Two tiles per stage halve the per-byte cost of everything
@@ -309,9 +115,6 @@ struct Shape {
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;   // control block + stages + alignment slack
   static constexpr int kAccCols = 2 * kNCap;                        // TMEM columns of one accumulator stage
   static constexpr int kSfCol = 2 * kAccCols;                       // scale region: A0, A1, token scales (one copy per MMA warp)
-  // K stages of the task's weights requested into L2 ahead of the shared-memory pipeline.  Measured on B200: any
-  // distance > 0 slows every token count down (the pipeline is not DRAM-latency bound), so the default is off.
-  static constexpr int kPrefetchAhead = 0;
   static_assert(kSfCol + 16 <= (int)kTmemCols, "TMEM budget");
   static_assert(kStages >= 3, "pipeline too shallow");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -381,7 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  Waiter waiter{ctl, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), kLayer, warp};
+  Waiter waiter{&ctl->abort_flag, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), kLayer, warp};
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------------ producer
@@ -391,9 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       uint32_t stage = 0, phase = 0;
       const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
       const uint32_t a0 = smem_u32(a_base), b0 = smem_u32(b_base), sf0 = smem_u32(sf_base);
-      const int ab = MMOE_EXPERIMENTS ? p.ablate : 0;
       bool ok = true;
-      TR_DECL(tr_wait); TR_DECL(tr_issue); TR_DECL(tr_iters); TR_DECL(tr_blocked); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
         const int tile_idx = static_cast<int>(task / p.n_blocks);
         const int nb = static_cast<int>(task - (int64_t)tile_idx * p.n_blocks);
@@ -403,13 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int n16 = (tile.n_valid + 15) & ~15;
         const int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : (n16 <= 80 ? 3 : 4)));   // never above kBoxRows
         const uint32_t box_rows = box_sel == 3 ? 80u : (box_sel == 4 ? 128u : (16u << box_sel));
-#if MMOE_EXPERIMENTS
-        const CUtensorMap* wmap = shared ? &p.map_w_shared : ((ab & 128) ? &p.map_w_routed_packed : &p.map_w_routed);
-        const int kdiv = (!shared && (ab & 128)) ? 2 : 1;      // byte coordinates of the packed view
-#else
         const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
-        constexpr int kdiv = 1;
-#endif
         const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
         const int e = shared ? 0 : tile.expert;
         // The 256 stored weight rows of the task.  Layer 1 reads W13 in its stored order [g0..7, u0..7, g8..15, ...]
@@ -425,46 +220,23 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int64_t tsf_rows = shared ? p.tsf_rows_shared : p.tsf_rows_routed;
         const int32_t* tsf = (shared ? p.tsf_shared : p.tsf_routed) + (int64_t)tile.sf_chunk * kChunkRows;
         const uint32_t a_tx = shared ? 2 * kTileRows * kTileK : kTileRows * kTileK;   // packed FP4 counts its global bytes
-        uint32_t tx = 0;
-        if (!(ab & 32)) tx += a_tx;
-        if (!(ab & 4)) tx += box_rows * kTileK;
-        if (!(ab & 1)) tx += 1024;
-        if (!(ab & 2)) tx += 512;
+        const uint32_t tx = a_tx + box_rows * kTileK + 1024 + 512;
         int k0 = 0;
         for (int kb = 0; kb < k_stages; ++kb, k0 += kTileK, wsf += p.rows_per_expert, tsf += tsf_rows) {
-          TR_ADD(tr_issue);
-#if MMOE_TRACE
-          if (!mbar_test_wait(empty0 + 8 * stage, phase ^ 1u)) ++tr_blocked;
-#endif
           if (!waiter.wait(empty0 + 8 * stage, phase ^ 1u)) { ok = false; break; }
-          TR_ADD(tr_wait);
           const uint32_t bar = full0 + 8 * stage;
-          if (tx == 0) { mbar_arrive(bar); } else { mbar_expect_tx(bar, tx); }
+          mbar_expect_tx(bar, tx);
           const uint32_t a_dst = a0 + stage * S::kABytes;
           const uint32_t sf_dst = sf0 + stage * S::kSfBytes;
-          if (!(ab & 32)) {
-            if (kLayer == 1) tma_load_5d(a_dst, wmap, k0 / kdiv, 0, group, 0, slice, bar);
-            else tma_load_3d(a_dst, wmap, k0 / kdiv, row, slice, bar);
-            // ask DRAM for a later K stage of this task now: it needs no shared memory, only L2
-            if (MMOE_EXPERIMENTS && p.prefetch_ahead > 0 && kb + p.prefetch_ahead < k_stages) {
-              if (kLayer == 1) tma_prefetch_5d(wmap, k0 + p.prefetch_ahead * kTileK, 0, group, 0, slice);
-              else tma_prefetch_3d(wmap, k0 + p.prefetch_ahead * kTileK, row, slice);
-            }
-          }
-          // layer 1: raw scales of the 256 stored rows, permuted by warp 6; layer 2: two chunks already in order
-          if (!(ab & 1)) bulk_load(sf_dst + (kLayer == 1 && !S::kSfInPlace ? 3 * 512 : 0), wsf, 1024, bar);
-          if (!(ab & 4)) tma_load_2d(b0 + stage * S::kBBytes, tmap, k0, tile.row0, bar);
-          if (!(ab & 2)) bulk_load(sf_dst + 2 * 512, tsf, 512, bar);
+          if (kLayer == 1) tma_load_5d(a_dst, wmap, k0, 0, group, 0, slice, bar);
+          else tma_load_3d(a_dst, wmap, k0, row, slice, bar);
+          // layer 1: raw scales of the 256 stored rows, permuted by the MMA warps; layer 2: two chunks already in order
+          bulk_load(sf_dst + (kLayer == 1 && !S::kSfInPlace ? 3 * 512 : 0), wsf, 1024, bar);
+          tma_load_2d(b0 + stage * S::kBBytes, tmap, k0, tile.row0, bar);
+          bulk_load(sf_dst + 2 * 512, tsf, 512, bar);
           if (++stage == num_stages) { stage = 0; phase ^= 1u; }
-#if MMOE_TRACE
-          ++tr_iters;
-#endif
         }
       }
-#if MMOE_TRACE
-      TR_ADD(tr_issue);
-      if (blockIdx.x == 0) printf("L%d producer: iters %lld wait_empty %lld issue %lld blocked %lld\n", kLayer, tr_iters, tr_wait, tr_issue, tr_blocked);
-#endif
     }
   } else if (warp == 1 || warp == 6) {
     // ------------------------------------------------------------------------------------------------ MMA issuers
@@ -481,16 +253,15 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       bool ok = true;
       const uint32_t ready0 = smem_u32(&ctl->full[0]);
       const uint32_t empty0 = smem_u32(&ctl->empty[0]);
-      const uint64_t sw128_hi = (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-      const uint64_t sf_hi = (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
+      const uint64_t sw128_hi = desc_hi_sw128();
+      const uint64_t sf_hi = desc_hi_sf(128);
       // layer 1: the four 8-row groups of a weight tile's scales sit 256 bytes apart (see the rearrangement below)
-      const uint64_t sfa_hi = S::kSfInPlace ? ((static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 46)) : sf_hi;
+      const uint64_t sfa_hi = S::kSfInPlace ? desc_hi_sf(256) : sf_hi;
       const uint32_t a_lo0 = ((smem_u32(a_base) & 0x3FFFFu) >> 4) + h * (kTileRows * kTileK >> 4);
       const uint32_t b_lo0 = (smem_u32(b_base) & 0x3FFFFu) >> 4;
       const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
       const uint32_t sfa_col = tmem_base + S::kSfCol + 4 * h;
       const uint32_t sfb_col = tmem_base + S::kSfCol + 8 + 4 * h;
-      const int ab = MMOE_EXPERIMENTS ? p.ablate : 0;
       int src[4];                                    // layer 1: source word of the 4 destination words this lane writes
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -499,26 +270,18 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         const int r = 16 * ((m & 63) >> 3) + 8 * h + (m & 7);   // stored row inside its 128-row block
         src[t] = 128 * (m >> 6) + 4 * (r & 31) + (r >> 5);
       }
-      TR_DECL(tr_wte); TR_DECL(tr_wfull); TR_DECL(tr_issue); TR_DECL(tr_blocked); TR_T0();
       for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
         const Tile tile = tiles[task / p.n_blocks];
         const bool shared = tile.expert == kSharedExpert;
         const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
-        TR_ADD(tr_issue);
         if (!waiter.wait_warp(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
-        TR_ADD(tr_wte);
         tc_fence_after();
         const uint32_t n = static_cast<uint32_t>((tile.n_valid + 15) & ~15);
-        const uint32_t idesc0 = make_idesc(shared ? 0u : 5u, n, 0);
+        const uint32_t idesc0 = make_idesc(shared ? 0u : 5u, 0u, n, 0);
         const uint32_t d = tmem_base + acc_stage * S::kAccCols + h * S::kNCap;
         const uint32_t sfb = sfb_col + tile.sf_col;
         for (int kb = 0; kb < k_stages; ++kb) {
-          TR_ADD(tr_issue);
-#if MMOE_TRACE
-          if (!mbar_test_wait(ready0 + 8 * stage, phase)) ++tr_blocked;
-#endif
           if (!waiter.wait_warp(ready0 + 8 * stage, phase)) { ok = false; break; }
-          TR_ADD(tr_wfull);
           const uint32_t a_lo = a_lo0 + stage * (S::kABytes >> 4);
           const uint32_t b_lo = b_lo0 + stage * (S::kBBytes >> 4);
           const uint32_t sf_lo = sf_lo0 + stage * (S::kSfBytes >> 4);
@@ -549,19 +312,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
             __syncwarp();
           }
           if (elect_one()) {
-            if (!(ab & 8)) {
-              tc_cp_sf(sfa_col, sfa_hi | (sf_lo + (S::kSfInPlace ? 8 : 32) * h));
-              tc_cp_sf(sfb_col, sf_hi | (sf_lo + 64));
-            }
-            if (!(ab & 16)) {
+            tc_cp_sf(sfa_col, sfa_hi | (sf_lo + (S::kSfInPlace ? 8 : 32) * h));
+            tc_cp_sf(sfb_col, sf_hi | (sf_lo + 64));
 #pragma unroll
-              for (int k = 0; k < kTileK / 32; ++k)
-                tc_mma(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
-                       idesc0 + k * ((1u << 4) | (1u << 29)),               // scale byte k of both operands
-                       sfa_col, sfb, (kb | k) != 0 ? 1u : 0u);
-            }
-            if (ab & 64) mbar_arrive(empty0 + 8 * stage);
-            else tc_commit(empty0 + 8 * stage);       // shared memory of this stage is free once these MMAs retire
+            for (int k = 0; k < kTileK / 32; ++k)
+              tc_mma(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
+                     idesc0 + k * ((1u << 4) | (1u << 29)),               // scale byte k of both operands
+                     sfa_col, sfb, (kb | k) != 0 ? 1u : 0u);
+            tc_commit(empty0 + 8 * stage);            // shared memory of this stage is free once these MMAs retire
           }
           __syncwarp();
           if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -569,10 +327,6 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
         if (ok && elect_one()) tc_commit(smem_u32(&ctl->tmem_full[acc_stage]));
         __syncwarp();
       }
-#if MMOE_TRACE
-      TR_ADD(tr_issue);
-      if (blockIdx.x == 0 && lane == 0) printf("L%d mma%d: tasks %u wait_tmem_empty %lld wait_full %lld issue %lld blocked %lld\n", kLayer, h, it, tr_wte, tr_wfull, tr_issue, tr_blocked);
-#endif
     }
   } else {
     // ------------------------------------------------------------------------------------------------ epilogue
@@ -580,7 +334,6 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     uint32_t it = 0;
     bool ok = true;
-    TR_DECL(tr_wfull); TR_DECL(tr_work); TR_T0();
     for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
       const Tile tile = tiles[task / p.n_blocks];
       const int nb = static_cast<int>(task % p.n_blocks);
@@ -606,9 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
           }
         }
       }
-      TR_ADD(tr_work);
       if (!waiter.wait_warp(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { ok = false; break; }
-      TR_ADD(tr_wfull);
       tc_fence_after();
       const uint32_t d0 = tmem_base + lane_sel + acc_stage * S::kAccCols;
       const int n16 = (tile.n_valid + 15) & ~15;
@@ -688,10 +439,6 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->tmem_empty[acc_stage]));
     }
-#if MMOE_TRACE
-    TR_ADD(tr_work);
-    if (blockIdx.x == 0 && threadIdx.x == 64) printf("L%d epilogue: tasks %u wait_tmem_full %lld work %lld\n", kLayer, it, tr_wfull, tr_work);
-#endif
   }
 
   // ---------------------------------------------------------------------------------------------------- teardown
@@ -716,41 +463,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
-int g_num_sms = 0;
-int g_tune_prefetch = -1;   // < 0: the compiled default of each kernel
-int g_tune_stages = 0;      // 0: every stage that fits
-int g_tune_ablate = 0;
+constexpr int kMaxDevices = 64;
+int g_num_sms[kMaxDevices] = {};   // per device, 0 = mmoe_prepare() has not run there
+int g_tune_stages = 0;             // 0: every stage that fits
+int g_orientation = 0;             // 0: chosen per call, 1: weights-as-A always, 2: tokens-as-A wherever the geometry allows
 
-// token rows: 2-D map [rows, K] of E4M3 bytes
-int make_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows, uint32_t box_rows,
-             bool weights) {
-  const cuuint64_t dims[2] = {k_elems, rows};
-  const cuuint64_t strides[1] = {fp4 ? k_elems / 2 : k_elems};
-  const cuuint32_t box[2] = {kTileK, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
-                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B,
-                              weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
-}
-
-// weights: 3-D map [slices, rows per slice, K]; a plain tensor is one slice
-int make_weight_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows_total,
-                    int64_t slice_stride) {
-  const uint64_t row_bytes = fp4 ? k_elems / 2 : k_elems;
-  const uint64_t slices = slice_stride > 0 ? 2 : 1;
-  const uint64_t rows = rows_total / slices;
-  const cuuint64_t dims[3] = {k_elems, rows, slices};
-  const cuuint64_t strides[2] = {row_bytes, slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes};
-  const cuuint32_t box[3] = {kTileK, 2 * kTileRows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
-                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
 }
 
 // W13 (stored rows [g0..7, u0..7, g8..15, ...]): 5-D map [slices, gate/up, groups of 16 rows, row in group of 8, K];
@@ -771,33 +492,6 @@ int make_w13_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems,
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
-// experiment only: the packed FP4 bytes of a weight tensor as a plain byte tensor (no expansion), same box geometry
-int make_packed_map(CUtensorMap* map, bool w13, const void* base, uint64_t k_elems, uint64_t rows_total, int64_t slice_stride) {
-  const uint64_t row_bytes = k_elems / 2;
-  const uint64_t slices = slice_stride > 0 ? 2 : 1;
-  const uint64_t rows = rows_total / slices;
-  const uint64_t sl = slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes;
-  CUresult r;
-  if (w13) {
-    const cuuint64_t dims[5] = {row_bytes, 8, rows / 16, 2, slices};
-    const cuuint64_t strides[4] = {row_bytes, 16 * row_bytes, 8 * row_bytes, sl};
-    const cuuint32_t box[5] = {kTileK / 2, 8, 16, 2, 1};
-    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void*>(base), dims, strides, box, estr,
-                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  } else {
-    const cuuint64_t dims[3] = {row_bytes, rows, slices};
-    const cuuint64_t strides[2] = {row_bytes, sl};
-    const cuuint32_t box[3] = {kTileK / 2, 2 * kTileRows, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  }
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
-}
-
 template <int kLayer, int kBoxRows>
 cudaError_t prepare_one() {
   cudaError_t e = cudaFuncSetAttribute(umma_kernel<kLayer, kBoxRows, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -813,10 +507,9 @@ cudaError_t launch_one(const UmmaParams& p0, cudaStream_t s) {
   using S = Shape<kLayer, kBoxRows>;
   UmmaParams p = p0;
   p.num_stages = g_tune_stages > 0 && g_tune_stages < S::kStages ? g_tune_stages : S::kStages;
-  p.prefetch_ahead = g_tune_prefetch >= 0 ? g_tune_prefetch : S::kPrefetchAhead;
-  p.ablate = g_tune_ablate;
-  if (kLayer == 2 && p.fused_return) umma_kernel<2, kBoxRows, true><<<g_num_sms, kThreads, Shape<2, kBoxRows>::kSmemBytes, s>>>(p);
-  else umma_kernel<kLayer, kBoxRows, false><<<g_num_sms, kThreads, S::kSmemBytes, s>>>(p);
+  const int grid = tc_num_sms();
+  if (kLayer == 2 && p.fused_return) umma_kernel<2, kBoxRows, true><<<grid, kThreads, Shape<2, kBoxRows>::kSmemBytes, s>>>(p);
+  else umma_kernel<kLayer, kBoxRows, false><<<grid, kThreads, S::kSmemBytes, s>>>(p);
   return cudaGetLastError();
 }
 
@@ -833,14 +526,134 @@ cudaError_t launch_layer(const UmmaParams& p, int box, cudaStream_t s) {
   }
 }
 
-}  // namespace
+// tokens-as-A form: both layers through mmoe_umma_tm.cu
+cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, bool has_shared,
+                              int64_t timeout_ns, cudaStream_t s) {
+  const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
+  TmParams p1{};
+  int bad = 0;
+  bad |= make_weight_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride, 192);
+  if (has_shared) bad |= make_weight_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0, 192);
+  else p1.map_w_shared = p1.map_w_routed;
+  const uint32_t kBoxes[2] = {64, 128};
+  // a 128-row box may start up to 127 rows before the end of the token matrix; the rows past it are workspace bytes of
+  // the regions that follow (never stored anywhere: they only feed accumulator lanes of rows that do not exist)
+  const uint64_t x_rows = (uint64_t)c.geo.num_max_tokens + 128;
+  for (int b = 0; b < 2; ++b) {
+    bad |= make_token_map(&p1.map_tok_routed[b], c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b]);
+    if (has_shared) bad |= make_token_map(&p1.map_tok_shared[b], c.ws + c.lay.x, h, x_rows, kBoxes[b]);
+    else p1.map_tok_shared[b] = p1.map_tok_routed[b];
+  }
+  if (bad) return cudaErrorInvalidValue;
+  p1.plan = c.ws + c.lay.plan;
+  p1.wsf_routed = static_cast<const int32_t*>(w.w13_sf);
+  p1.wsf_shared = static_cast<const int32_t*>(w.shared_w13_sf);
+  p1.tsf_routed = c.at<int32_t>(c.lay.pool_sf);
+  p1.tsf_shared = c.at<int32_t>(c.lay.shared_x_sf);
+  p1.tsf_rows_routed = c.lay.pool_sf_rows;
+  p1.tsf_rows_shared = c.lay.shared_sf_rows;
+  p1.act_routed = c.at<uint8_t>(c.lay.act_x);
+  p1.act_shared = c.at<uint8_t>(c.lay.shared_act_x);
+  p1.act_sf_routed = c.at<uint8_t>(c.lay.act_sf);
+  p1.act_sf_shared = c.at<uint8_t>(c.lay.shared_act_sf);
+  p1.act_sf_rows_routed = c.lay.pool_sf_rows;
+  p1.act_sf_rows_shared = c.lay.shared_sf_rows;
+  p1.pool_w = c.at<float>(c.lay.pool_w);
+  p1.status = c.at<int32_t>(c.lay.status);
+  p1.timeout_ns = timeout_ns;
+  p1.e_local = el;
+  p1.num_ranks = c.geo.num_ranks;
+  p1.k_dim = h;
+  p1.rows_per_expert = 2 * inter;
+  p1.routed_sliced = w.w13_slice_stride > 0 ? 1 : 0;
+  p1.hidden = h;
+  p1.inter = inter;
+  p1.clamp = o.activation_clamp;
+  p1.fast_math = o.fast_math;
+  p1.has_shared_weights = has_shared ? 1 : 0;
+  p1.tile_select = c.tile_select;
+  p1.early_shared_first = c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens);
+  p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
 
-void set_tuning(int prefetch_ahead, int max_stages) {
-  g_tune_prefetch = prefetch_ahead;
-  g_tune_stages = max_stages & 0xFFFF;
-  g_tune_ablate = max_stages >> 16;       // experiments only: high half-word = ablation mask
+  TmParams p2 = p1;
+  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride, 192);
+  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0, 192);
+  else p2.map_w_shared = p2.map_w_routed;
+  for (int b = 0; b < 2; ++b) {
+    bad |= make_token_map(&p2.map_tok_routed[b], c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b]);
+    if (has_shared) bad |= make_token_map(&p2.map_tok_shared[b], c.ws + c.lay.shared_act_x, inter, x_rows, kBoxes[b]);
+    else p2.map_tok_shared[b] = p2.map_tok_routed[b];
+  }
+  if (bad) return cudaErrorInvalidValue;
+  p2.wsf_routed = static_cast<const int32_t*>(w.w2_sf);
+  p2.wsf_shared = static_cast<const int32_t*>(w.shared_w2_sf);
+  p2.tsf_routed = c.at<int32_t>(c.lay.act_sf);
+  p2.tsf_shared = c.at<int32_t>(c.lay.shared_act_sf);
+  p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
+  p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
+  p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
+  bool fused = false;
+  if (c.peer_ws != nullptr && c.geo.num_ranks > 1 && c.tile_select != 2) {
+    fused = true;
+    p2.ep_me = c.geo.rank;
+    p2.ep_totals = reinterpret_cast<const int32_t*>(c.ws + c.lay.ep_sync + ep_totals_offset());
+    for (int r = 0; r < c.geo.num_ranks; ++r)
+      p2.ep_ret_recv[r] = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(const_cast<void*>(c.peer_ws[r])) + c.lay.ret_recv);
+  }
+  p2.k_dim = inter;
+  p2.rows_per_expert = h;
+  p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
+
+  const int mask = o.layer_mask == 0 ? 3 : o.layer_mask;
+  cudaError_t e = cudaSuccess;
+  if (mask & 1) e = tm_launch(1, false, p1, s);
+  if (e != cudaSuccess) return e;
+  if (mask & 2) e = tm_launch(2, fused, p2, s);
+  return e;
 }
 
+}  // namespace
+
+int tc_num_sms() {
+  const int dev = current_device();
+  return dev < 0 ? 0 : g_num_sms[dev];
+}
+bool tc_ready() { return g_encode != nullptr && tc_num_sms() > 0; }
+
+void set_tuning(int max_stages, int orientation) {
+  g_tune_stages = max_stages;
+  g_orientation = orientation;
+}
+int tuned_orientation() { return g_orientation; }
+
+int make_token_map(CUtensorMap* map, const void* base, uint64_t k_elems, uint64_t rows, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {k_elems, rows};
+  const cuuint64_t strides[1] = {k_elems};
+  const cuuint32_t box[2] = {kTileK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+int make_weight_map(CUtensorMap* map, bool fp4, const void* base, uint64_t k_elems, uint64_t rows_total,
+                    int64_t slice_stride, uint32_t box_rows) {
+  const uint64_t row_bytes = fp4 ? k_elems / 2 : k_elems;
+  const uint64_t slices = slice_stride > 0 ? 2 : 1;
+  const uint64_t rows = rows_total / slices;
+  const cuuint64_t dims[3] = {k_elems, rows, slices};
+  const cuuint64_t strides[2] = {row_bytes, slice_stride > 0 ? static_cast<uint64_t>(slice_stride) : rows * row_bytes};
+  const cuuint32_t box[3] = {kTileK, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+// Once per device (the dynamic shared-memory limits are per device) and outside stream capture.
 int prepare_umma(const MmoeGeometry& geo) {
   (void)geo;
   if (g_encode == nullptr) {
@@ -851,9 +664,11 @@ int prepare_umma(const MmoeGeometry& geo) {
       return MMOE_ERR_CUDA;
     g_encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return MMOE_ERR_CUDA;
-  if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MMOE_ERR_CUDA;
+  const int dev = current_device();
+  if (dev < 0) return MMOE_ERR_CUDA;
+  if (g_num_sms[dev] > 0) return MMOE_OK;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MMOE_ERR_CUDA;
   cudaError_t e = cudaSuccess;
   if (e == cudaSuccess) e = prepare_one<1, 16>();
   if (e == cudaSuccess) e = prepare_one<1, 32>();
@@ -865,30 +680,31 @@ int prepare_umma(const MmoeGeometry& geo) {
   if (e == cudaSuccess) e = prepare_one<2, 64>();
   if (e == cudaSuccess) e = prepare_one<2, 80>();
   if (e == cudaSuccess) e = prepare_one<2, 128>();
-  return e == cudaSuccess ? MMOE_OK : MMOE_ERR_CUDA;
+  if (e == cudaSuccess) e = tm_prepare();
+  if (e != cudaSuccess) return MMOE_ERR_CUDA;
+  g_num_sms[dev] = sms;
+  return MMOE_OK;
 }
 
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m,
                                 cudaStream_t s) {
-  if (g_encode == nullptr || g_num_sms == 0) return cudaErrorNotReady;
+  if (!tc_ready()) return cudaErrorNotReady;
   const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
   const int box = box_rows_of(block_m);
   const bool has_shared = c.geo.num_shared_experts > 0 && w.shared_w13 != nullptr && m > 0;
   const int64_t timeout_ns = (o.timeout_ms > 0 ? (int64_t)o.timeout_ms : 2000) * 1000000ll;
+  if (c.token_major) return launch_experts_tm(c, w, o, m, has_shared, timeout_ns, s);
 
   UmmaParams p1{};
   int bad = 0;
   bad |= make_w13_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
   if (has_shared) bad |= make_w13_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
   else p1.map_w_shared = p1.map_w_routed;
-#if MMOE_EXPERIMENTS
-  bad |= make_packed_map(&p1.map_w_routed_packed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
-#endif
   // token maps: one per box size a tile of this launch can pick (never above the kernel's own box)
   const uint32_t kBoxes[5] = {16, 32, 64, 80, 128};
   for (int b = 0; b < 5 && (int)kBoxes[b] <= box; ++b) {
-    bad |= make_map(&p1.map_tok_routed_box[b], false, c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b], false);
-    if (has_shared) bad |= make_map(&p1.map_tok_shared_box[b], false, c.ws + c.lay.x, h, c.geo.num_max_tokens, kBoxes[b], false);
+    bad |= make_token_map(&p1.map_tok_routed_box[b], c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b]);
+    if (has_shared) bad |= make_token_map(&p1.map_tok_shared_box[b], c.ws + c.lay.x, h, c.geo.num_max_tokens, kBoxes[b]);
     else p1.map_tok_shared_box[b] = p1.map_tok_routed_box[b];
   }
   if (bad) return cudaErrorInvalidValue;
@@ -924,15 +740,12 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
 
   UmmaParams p2 = p1;
-  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
-  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0);
+  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride, 2 * kTileRows);
+  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0, 2 * kTileRows);
   else p2.map_w_shared = p2.map_w_routed;
-#if MMOE_EXPERIMENTS
-  bad |= make_packed_map(&p2.map_w_routed_packed, false, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride);
-#endif
   for (int b = 0; b < 5 && (int)kBoxes[b] <= box; ++b) {
-    bad |= make_map(&p2.map_tok_routed_box[b], false, c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b], false);
-    if (has_shared) bad |= make_map(&p2.map_tok_shared_box[b], false, c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, kBoxes[b], false);
+    bad |= make_token_map(&p2.map_tok_routed_box[b], c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b]);
+    if (has_shared) bad |= make_token_map(&p2.map_tok_shared_box[b], c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, kBoxes[b]);
     else p2.map_tok_shared_box[b] = p2.map_tok_routed_box[b];
   }
   if (bad) return cudaErrorInvalidValue;
