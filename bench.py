@@ -449,7 +449,7 @@ def main():
     ap.add_argument("--ep-transport", default="peer", choices=("peer", "peer-unfused", "nccl"),
                     help="N > 1: device-side NVLink exchange with the write-back fused into GEMM2 (default), the same "
                          "with a separate copy kernel, or the host-driven NCCL all-to-allv")
-    ap.add_argument("--orientation", type=int, default=0, choices=(0, 1, 2),
+    ap.add_argument("--orientation", type=int, default=0, choices=(0, 1, 2, 3),
                     help="grouped-GEMM kernel family: 0 chosen per call, 1 weights-as-A, 2 tokens-as-A")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -72,13 +72,15 @@ def test_every_block_m_variant(bm):
 
 @pytest.mark.parametrize("geom", [dict(hidden=512, inter=256, num_experts=8, num_topk=2),
                                   dict(hidden=1024, inter=384, num_experts=4, num_topk=2)])
+@pytest.mark.parametrize("orientation", [2, 3])
 @pytest.mark.parametrize("bm", [16, 64, 128, 192, 240])
-def test_tokens_as_a_kernels_every_block_m(geom, bm):
+def test_tokens_as_a_kernels_every_block_m(geom, bm, orientation):
     """The tokens-as-A kernel family forced on (it is otherwise chosen from the expected rows per expert): tiles of up
     to 128 rows under every BLOCK_M pool layout, weight blocks of 192 stored rows with the short last block of a half
     (64 or 128 rows, loaded through the shifted box), scale chunks starting at row 0 and 64 of a 128-row chunk, the
-    shared expert's tiles, masked routes and experts without tokens.  Against the oracle, and against the weights-as-A
-    kernels on the same inputs."""
+    shared expert's tiles, masked routes and experts without tokens.  Orientation 3 runs them on CTA pairs (two tiles of
+    an expert per task, an empty second tile where an expert has an odd number; BLOCK_M < 128 falls back to single
+    CTAs).  Against the oracle, and against the weights-as-A kernels on the same inputs."""
     from vllm_plugin_b200 import api
     layer = H.make_layer(shared=True, seed=21, **geom)
     m = 600
@@ -87,7 +89,7 @@ def test_tokens_as_a_kernels_every_block_m(geom, bm):
     ids[ids == 1] = -1                                      # an expert that receives nothing
     api.set_kernel_options(block_m=bm)
     try:
-        y_tm, buf = H.run_layer(layer, hid, ids, w, orientation=2)
+        y_tm, buf = H.run_layer(layer, hid, ids, w, orientation=orientation)
         assert buf.plan_tables()[0]["block_m"] == bm
         y_sa, _ = H.run_layer(layer, hid, ids, w, orientation=1)
     finally:
@@ -99,15 +101,16 @@ def test_tokens_as_a_kernels_every_block_m(geom, bm):
     assert diff <= 2e-2, f"the two kernel families differ by {diff}"
 
 
+@pytest.mark.parametrize("orientation", [2, 3])
 @pytest.mark.parametrize("m", [1, 40, 129, 700])
-def test_tokens_as_a_kernels_token_counts_and_options(m):
+def test_tokens_as_a_kernels_token_counts_and_options(m, orientation):
     """Forced tokens-as-A kernels over small and ragged token counts (tiles of 1..128 rows, the 64-row token box), with
     the two-slice weight form, without clamp, and with the IEEE sigmoid."""
     layer = H.make_layer(shared=True, seed=23, hidden=1024, inter=512, num_experts=4, num_topk=2)
     hid = (O.make_hidden(m, layer.hidden, 1).float() * 3).to(torch.bfloat16)
     ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 2, mask_frac=0.1 if m > 1 else 0.0)
     for clamp, fast, localized in ((10.0, True, False), (None, False, True)):
-        y, _ = H.run_layer(layer, hid, ids, w, clamp=clamp, fast_math=fast, localized=localized, orientation=2)
+        y, _ = H.run_layer(layer, hid, ids, w, clamp=clamp, fast_math=fast, localized=localized, orientation=orientation)
         assert_parity(y, H.oracle_layer(layer, hid, ids, w, clamp=clamp), f"m {m} clamp {clamp} fast {fast}")
 
 

@@ -36,7 +36,7 @@ class KernelOptions:
                                 # stream; False = one stream, separate copy kernel after GEMM2 (same result)
     orientation: int = 0        # grouped-GEMM kernel family: 0 = chosen per call from the expected rows per expert,
                                 # 1 = weights-as-A (small token counts) always, 2 = tokens-as-A wherever the geometry
-                                # allows; every rank of a group must use the same value
+                                # allows, 3 = tokens-as-A on CTA pairs; every rank of a group must use the same value
 
 
 _kernel_options = KernelOptions()

@@ -100,20 +100,25 @@ int make_ctx(const MmoeGeometry* g, void* ws, mmoe::Ctx* c) {
   return MMOE_OK;
 }
 
-// Which kernel family runs a tile list, hence how the list is cut (tiles of up to 128 rows for the tokens-as-A
-// kernels).  A pure function of the call's geometry, token count and BLOCK_M, so that the planning step and the GEMM
-// launches of one call agree without talking to each other.  `early_shared`: the shared expert's tiles planned ahead
-// of the routed ones (tile_select 2); otherwise the routed tiles and the shared tiles planned with them.
-bool choose_token_major(const MmoeGeometry* g, int m, int block_m, bool early_shared) {
-  const bool fits = g->intermediate >= 192 && g->hidden / 2 >= 192;      // a half of each weight matrix holds a 192-row box
+// Which kernel family runs a tile list, hence how the list is cut.  A pure function of the call's geometry, token
+// count and BLOCK_M, so that the planning step and the GEMM launches of one call agree without talking to each other.
+// `early_shared`: the shared expert's tiles planned ahead of the routed ones (tile_select 2); otherwise the routed tiles
+// and the shared tiles planned with them.
+int choose_family(const MmoeGeometry* g, int m, int block_m, bool early_shared) {
+  // a half of each weight matrix must hold a 192-row box (more than one for the short last block of a CTA pair)
+  const bool fits = g->intermediate >= 192 && g->hidden / 2 >= 192;
+  const bool pair_ok = fits && block_m >= 128;        // two scale chunks per pool block: one per half of a pair
   const int forced = mmoe::tuned_orientation();
-  if (!fits || forced == 1) return false;
-  if (forced == 2) return true;
-  if (early_shared) return m > 128;
+  if (!fits || forced == 1) return mmoe::kFamilyWeightsAsA;
+  if (forced == 2 || (forced == 3 && !pair_ok)) return mmoe::kFamilyTokensAsA;
+  if (forced == 3) return mmoe::kFamilyTokensAsAPair;
+  // CTA pairs are never chosen automatically: measured on B200 at 120 / 240 / 480 rows per expert a pair step takes
+  // 1.90 / 1.20 / 1.08 ms against 1.38 / 1.15 / 1.08 ms on single CTAs (the issuing thread pays two commits per stage)
+  if (early_shared) return m > 128 ? mmoe::kFamilyTokensAsA : mmoe::kFamilyWeightsAsA;
   // expected rows per expert (the quantity BLOCK_M is chosen from): below ~80 the weights-as-A kernels, whose cost
-  // follows the token count, win; above it the tensor-bound tokens-as-A form does
+  // follows the token count, win (and stream more weight bytes per stage when the call is HBM-bound)
   const double expected = (double)m * g->num_ranks * g->num_topk / g->num_experts;
-  return block_m >= 64 && expected >= 80.0;
+  return block_m >= 64 && expected >= 80.0 ? mmoe::kFamilyTokensAsA : mmoe::kFamilyWeightsAsA;
 }
 
 int check_tokens(const MmoeGeometry* g, int m) {
@@ -138,7 +143,7 @@ int mmoe_abi_version(void) { return 2; }
 
 int mmoe_set_tuning(int32_t max_stages, int32_t orientation) {
   if (max_stages < 0 || max_stages == 1) return fail(MMOE_ERR_INVALID_ARGUMENT, "max_stages=%d must be 0 or >= 2", max_stages);
-  if (orientation < 0 || orientation > 2) return fail(MMOE_ERR_INVALID_ARGUMENT, "orientation=%d outside [0, 2]", orientation);
+  if (orientation < 0 || orientation > 3) return fail(MMOE_ERR_INVALID_ARGUMENT, "orientation=%d outside [0, 3]", orientation);
   mmoe::set_tuning(max_stages, orientation);
   return MMOE_OK;
 }
@@ -376,7 +381,7 @@ int mmoe_dispatch_place(const MmoeGeometry* geo, void* workspace, int32_t num_to
   rc = check_tokens(geo, num_tokens);
   if (rc != MMOE_OK) return rc;
   if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
-  c.token_major = choose_token_major(geo, num_tokens, block_m, false);
+  c.family = choose_family(geo, num_tokens, block_m, false);
   cudaError_t e = mmoe::launch_plan_place(c, num_tokens, block_m, stats, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "dispatch_place launch");
 }
@@ -399,7 +404,7 @@ int mmoe_plan_shared(const MmoeGeometry* geo, void* workspace, int32_t num_token
   if (rc == MMOE_OK) rc = check_tokens(geo, num_tokens);
   if (rc != MMOE_OK) return rc;
   if (!valid_block_m(block_m)) return fail(MMOE_ERR_INVALID_ARGUMENT, "block_m=%d is not a BLOCK_M value", block_m);
-  c.token_major = choose_token_major(geo, num_tokens, block_m, true);
+  c.family = choose_family(geo, num_tokens, block_m, true);
   cudaError_t e = mmoe::launch_shared_plan(c, num_tokens, block_m, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "shared plan launch");
 }
@@ -461,7 +466,7 @@ int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* pee
     if (!mmoe::tc_ready()) return fail(MMOE_ERR_NOT_PREPARED, "mmoe_prepare() must run on this device before the first launch");
     c.peer_ws = peers;
     c.tile_select = tile_select;
-    c.token_major = choose_token_major(geo, num_tokens, block_m, tile_select == 2);
+    c.family = choose_family(geo, num_tokens, block_m, tile_select == 2);
     e = mmoe::launch_experts_umma(c, *weights, o, num_tokens, block_m, st);
     if (e == cudaSuccess && peers != nullptr) e = mmoe::launch_ep_signal_return(c, peers, timeout_ns, st);
   } else {
@@ -495,7 +500,7 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
       mmoe::Ctx c;
       int r = make_ctx(geo, workspace, &c);
       if (r != MMOE_OK) return r;
-      c.token_major = choose_token_major(geo, num_tokens, block_m, false);
+      c.family = choose_family(geo, num_tokens, block_m, false);
       cudaError_t e = mmoe::launch_route_plan_place_small(c, num_tokens, block_m, stats, static_cast<cudaStream_t>(st));
       return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "route/plan launch");
     }
@@ -579,7 +584,7 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   // ... while the shared expert, which needs only this rank's own tokens, runs both of its GEMMs here
   mmoe::Ctx c;
   rc = make_ctx(geo, workspace, &c);
-  if (rc == MMOE_OK) c.token_major = choose_token_major(geo, num_tokens, block_m, true);
+  if (rc == MMOE_OK) c.family = choose_family(geo, num_tokens, block_m, true);
   if (rc == MMOE_OK && mmoe::launch_shared_plan(c, num_tokens, block_m, main_stream) != cudaSuccess)
     rc = cuda_fail(cudaGetLastError(), "shared plan launch");
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 2);

@@ -20,9 +20,12 @@ constexpr int kMaxTileTokens = 112;  // largest UMMA N of one task
 // tiles at 80 rows: the 10 KB token slot buys a fifth pipeline stage.  192 / 240 keep 112 (the tensor-bound
 // expert-parallel shapes, where fewer and larger tiles matter more than pipeline depth).
 __host__ __device__ inline int max_tile_rows(int block_m) { return block_m <= 64 ? block_m : (block_m == 128 ? 80 : kMaxTileTokens); }
-// Tile cap of a launch: the tokens-as-A kernels take tiles of up to 128 rows whatever BLOCK_M is.
+// Kernel family of a launch, hence how its tile list is cut: weights-as-A kernels (tiles of at most max_tile_rows),
+// tokens-as-A kernels (tiles of up to 128 rows whatever BLOCK_M is), tokens-as-A kernels on CTA pairs (an even number of
+// tiles per expert: tiles 2j and 2j + 1 are the two halves of one pair task).
+enum { kFamilyWeightsAsA = 0, kFamilyTokensAsA = 1, kFamilyTokensAsAPair = 2 };
 constexpr int kTokenMajorTileRows = 128;
-__host__ __device__ inline int tile_cap(int block_m, bool token_major) { return token_major ? kTokenMajorTileRows : max_tile_rows(block_m); }
+__host__ __device__ inline int tile_cap(int block_m, int family) { return family != kFamilyWeightsAsA ? kTokenMajorTileRows : max_tile_rows(block_m); }
 // Scale-factor chunks (128 token rows each) reserved per pool block of a BLOCK_M variant: at least as many as the
 // tiles an expert's rows are cut into (ceil(n / max_tile_rows) <= ceil(n / block_m) * chunks_per_block for every n).
 __host__ __device__ inline int chunks_per_block(int block_m) { return block_m <= 64 ? 1 : (block_m <= 192 ? 2 : 3); }
@@ -131,13 +134,14 @@ __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(_
 // sigmoid, (gate*sig)*up*weight.  Operation order and roundings follow the reference's epilogue
 // (backend/kernel/epilogue.py:190-221).
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float swiglu_act(float gate_acc, float up_acc, float weight, float clamp, bool fast_math) {
+template <bool kFast>
+__device__ __forceinline__ float swiglu_act_t(float gate_acc, float up_acc, float weight, float clamp) {
   float g = bf16_round(gate_acc);
   float u = bf16_round(up_acc);
   g = fminf(g, clamp);                       // clamp is a BF16-representable value (or +inf)
   u = fminf(fmaxf(u, -clamp), clamp);
   float gated;
-  if (fast_math) {
+  if (kFast) {
     float e, r;
     const float t = __fmul_rn(-g, 1.4426950408889634f);
     asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(t));
@@ -148,6 +152,9 @@ __device__ __forceinline__ float swiglu_act(float gate_acc, float up_acc, float 
     gated = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
   }
   return __fmul_rn(__fmul_rn(gated, u), weight);
+}
+__device__ __forceinline__ float swiglu_act(float gate_acc, float up_acc, float weight, float clamp, bool fast_math) {
+  return fast_math ? swiglu_act_t<true>(gate_acc, up_acc, weight, clamp) : swiglu_act_t<false>(gate_acc, up_acc, weight, clamp);
 }
 
 // UE8M0 exponent of a non-negative amax by the integer-carry method (backend/kernel/ptx_g.py:235-241).
@@ -176,7 +183,7 @@ struct Ctx {             // resolved pointers of one call
   int kmax;              // min(k, E/R)
   const void* const* peer_ws = nullptr;   // set by the call that fuses the write-back into GEMM2 (EP > 1)
   int tile_select = 0;                    // 0: every tile of the plan, 1: routed tiles only, 2: the early shared tiles only
-  bool token_major = false;               // the tiles this call plans / runs are those of the tokens-as-A kernels (<= 128 rows)
+  int family = kFamilyWeightsAsA;         // kernel family the tiles this call plans / runs are cut for
   template <typename T> T* at(int64_t off) const { return reinterpret_cast<T*>(ws + off); }
 };
 
@@ -193,7 +200,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
 int prepare_umma(const MmoeGeometry& geo);   // returns an MMOE_* code
 bool tc_ready();                             // prepare_umma() has run on the current device
 void set_tuning(int max_stages, int orientation);
-int tuned_orientation();                     // 0: per call, 1: weights-as-A always, 2: tokens-as-A wherever the geometry allows
+int tuned_orientation();                     // 0: per call, 1: weights-as-A, 2: tokens-as-A, 3: tokens-as-A on CTA pairs
 cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_experts, int32_t* send_count,
                                int32_t* send_offset, int32_t* route_pos, int32_t* sorted_route, cudaStream_t s);
 int route_order_static_max_tokens();

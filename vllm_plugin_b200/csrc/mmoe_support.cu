@@ -346,7 +346,7 @@ cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s) {
 // Shared expert: the call's own tokens in blocks of block_m rows; the scale chunks were written by the quantiser in the
 // layout the engine prescribes (128-row chunks inside each block, backend/staging.py:85-95), so a tile is one chunk, or
 // one of its two 64-row halves when the chunk holds more rows than a tile may.
-__device__ int emit_shared_tiles(Tile* out, int n, int block_m, int cap) {
+__device__ int emit_shared_tiles(Tile* out, int n, int block_m, int cap, bool pair) {
   const int cpb = (block_m + kChunkRows - 1) / kChunkRows;
   int count = 0;
   for (int b = 0; b * block_m < n; ++b) {
@@ -366,21 +366,24 @@ __device__ int emit_shared_tiles(Tile* out, int n, int block_m, int cap) {
       }
     }
   }
+  if (pair && (count & 1)) out[count++] = Tile{kSharedExpert, 0, 0, 0, 0, {0, 0, 0}};   // empty second half of the last pair
   return count;
 }
 
 // Routed expert: its n rows are contiguous in the pool, starting on a block_m boundary (pool block `first_block`).
-// They are cut into ceil(n / max_tile_rows) equal tiles (rounded up to 16 rows) regardless of the block boundaries
-// inside the expert.  The scale chunks of the pool are this library's own: tile j of the expert uses chunk j of the
+// They are cut into ceil(n / cap) equal tiles (rounded up to 16 rows) regardless of the block boundaries inside the
+// expert; for CTA pairs into an even number of them (the last may be empty), so that tiles 2j and 2j + 1 of the table
+// always belong to the same expert.  The scale chunks of the pool are this library's own: tile j of the expert uses chunk j of the
 // chunks reserved for the expert's blocks.
-__device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int cap, int first_block, bool write) {
+__device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int cap, bool pair, int first_block,
+                          bool write) {
   if (n <= 0) return 0;
-  const int parts = (n + cap - 1) / cap;
+  const int parts = pair ? 2 * ((n + 2 * cap - 1) / (2 * cap)) : (n + cap - 1) / cap;
   const int step = parts == 1 ? n : ((n + parts - 1) / parts + 15) & ~15;
   if (write) {
     const int chunk0 = first_block * chunks_per_block(block_m);
     for (int j = 0; j < parts; ++j)
-      out[j] = Tile{expert, row_base + j * step, min(step, n - j * step), chunk0 + j, 0, {0, 0, 0}};
+      out[j] = Tile{expert, row_base + j * step, max(0, min(step, n - j * step)), chunk0 + j, 0, {0, 0, 0}};
   }
   return parts;
 }
@@ -388,16 +391,16 @@ __device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_
 // The shared expert's tiles depend only on the token count, so they can be planned (and run) before the routed
 // experts' receive counts are known: written at the tail of the tile table, counted in the header.
 __global__ void shared_plan_kernel(char* __restrict__ plan_base, int e_local, int num_ranks, int m, int block_m,
-                                   int cap, int64_t first_tile) {
+                                   int cap, int pair, int64_t first_tile) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     PlanView pv = plan_view(plan_base, e_local, num_ranks);
-    pv.hdr->num_early_shared_tiles = emit_shared_tiles(pv.tiles + first_tile, m, block_m, cap);
+    pv.hdr->num_early_shared_tiles = emit_shared_tiles(pv.tiles + first_tile, m, block_m, cap, pair != 0);
   }
 }
 
 __global__ void __launch_bounds__(1024) plan_kernel(
     char* __restrict__ plan_base, const int32_t* __restrict__ recv_count, int32_t* __restrict__ stats, int e_local,
-    int num_ranks, int block_m, int cap, int m, int has_shared) {
+    int num_ranks, int block_m, int cap, int pair, int m, int has_shared) {
   PlanView pv = plan_view(plan_base, e_local, num_ranks);
   __shared__ int32_t s_blocks[513], s_tiles[513];
   // per-source totals -> rank offsets in receive order
@@ -414,7 +417,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(
     for (int r = 0; r < num_ranks; ++r) tot += recv_count[r * e_local + e];
     pv.expert_total[e] = tot;
     s_blocks[e] = (tot + block_m - 1) / block_m;
-    s_tiles[e] = emit_tiles(nullptr, e, 0, tot, block_m, cap, 0, false);
+    s_tiles[e] = emit_tiles(nullptr, e, 0, tot, block_m, cap, pair != 0, 0, false);
     if (stats != nullptr) stats[e] += tot;      // cumulative per-expert receive statistics (dispatch.py:644-650)
   }
   __shared__ int32_t s_boff[514], s_toff[514];
@@ -432,7 +435,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(
     pv.hdr->num_tokens = m;
     // shared-expert tiles: the call's own tokens in blocks of block_m (chunk numbering of backend/staging.py:85-95)
     int ns = 0;
-    if (has_shared) ns = emit_shared_tiles(pv.tiles + rt, m, block_m, cap);
+    if (has_shared) ns = emit_shared_tiles(pv.tiles + rt, m, block_m, cap, pair != 0);
     pv.hdr->num_shared_tiles = ns;
   }
   __syncthreads();
@@ -452,7 +455,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(
       run += recv_count[r * e_local + e];
     }
     emit_tiles(pv.tiles + pv.expert_tile_off[e], e, pv.expert_block_off[e] * block_m, pv.expert_total[e], block_m, cap,
-               pv.expert_block_off[e], true);
+               pair != 0, pv.expert_block_off[e], true);
   }
 }
 
@@ -463,7 +466,7 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     const int64_t* __restrict__ topk_idx, int32_t* __restrict__ route_pos, int32_t* __restrict__ sorted_route,
     int32_t* __restrict__ send_count, int32_t* __restrict__ send_offset, int32_t* __restrict__ recv_count,
     char* __restrict__ plan_base, int32_t* __restrict__ stats, int32_t* __restrict__ status, int m, int k,
-    int num_experts, int block_m, int cap, int has_shared) {
+    int num_experts, int block_m, int cap, int pair, int has_shared) {
   extern __shared__ int32_t sm[];
   int32_t* ids = sm;                              // [m*k]
   int32_t* hist = sm + kSortChunkTokens * k;      // [E]
@@ -487,7 +490,7 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
     const int tot = hist[e];
     blocks[e] = (tot + block_m - 1) / block_m;
-    tiles_n[e] = emit_tiles(nullptr, e, 0, tot, block_m, cap, 0, false);
+    tiles_n[e] = emit_tiles(nullptr, e, 0, tot, block_m, cap, pair != 0, 0, false);
   }
   block_exclusive_scan(hist, off, num_experts);
   block_exclusive_scan(blocks, boff, num_experts);
@@ -499,7 +502,7 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     pv.hdr->total_recv = off[num_experts];
     pv.hdr->block_m = block_m;
     pv.hdr->num_tokens = m;
-    pv.hdr->num_shared_tiles = has_shared ? emit_shared_tiles(pv.tiles + to, m, block_m, cap) : 0;
+    pv.hdr->num_shared_tiles = has_shared ? emit_shared_tiles(pv.tiles + to, m, block_m, cap, pair != 0) : 0;
     pv.rank_off[0] = 0;
     pv.rank_off[1] = off[num_experts];
   }
@@ -527,7 +530,7 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     pv.seg_pool_start[e] = boff[e] * block_m;
     pv.seg_recv_start[e] = off[e];
     if (stats != nullptr) stats[e] += tot;
-    emit_tiles(pv.tiles + toff[e], e, boff[e] * block_m, tot, block_m, cap, boff[e], true);
+    emit_tiles(pv.tiles + toff[e], e, boff[e] * block_m, tot, block_m, cap, pair != 0, boff[e], true);
   }
   if (threadIdx.x == 0) {
     send_offset[num_experts] = off[num_experts];
@@ -605,8 +608,8 @@ cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int3
   route_plan_small_kernel<<<1, 1024, smem, s>>>(
       c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos), c.at<int32_t>(c.lay.sorted_route),
       c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.recv_count),
-      c.ws + c.lay.plan, stats, c.at<int32_t>(c.lay.status), m, k, e, block_m, tile_cap(block_m, c.token_major),
-      c.geo.num_shared_experts > 0);
+      c.ws + c.lay.plan, stats, c.at<int32_t>(c.lay.status), m, k, e, block_m, tile_cap(block_m, c.family),
+      c.family == kFamilyTokensAsAPair, c.geo.num_shared_experts > 0);
   place_kernel<<<148 * 2, 256, 0, s>>>(
       c.ws + c.lay.plan, c.at<uint4>(c.lay.x), c.at<int32_t>(c.lay.x_sf), c.at<float>(c.lay.topk_weights),
       c.at<int32_t>(c.lay.sorted_route), c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf),
@@ -617,14 +620,15 @@ cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int3
 
 cudaError_t launch_shared_plan(const Ctx& c, int m, int block_m, cudaStream_t s) {
   shared_plan_kernel<<<1, 32, 0, s>>>(c.ws + c.lay.plan, c.e_local, c.geo.num_ranks, m, block_m,
-                                      tile_cap(block_m, c.token_major), c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens));
+                                      tile_cap(block_m, c.family), c.family == kFamilyTokensAsAPair, c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens));
   return cudaGetLastError();
 }
 
 cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {
   const int R = c.geo.num_ranks;
   plan_kernel<<<1, 1024, 0, s>>>(c.ws + c.lay.plan, c.at<int32_t>(c.lay.recv_count), stats, c.e_local, R, block_m,
-                                 tile_cap(block_m, c.token_major), m, c.geo.num_shared_experts > 0);
+                                 tile_cap(block_m, c.family), c.family == kFamilyTokensAsAPair, m,
+                                 c.geo.num_shared_experts > 0);
   const bool direct = R == 1;
   place_kernel<<<148 * 8, 256, 0, s>>>(
       c.ws + c.lay.plan, direct ? c.at<uint4>(c.lay.x) : c.at<uint4>(c.lay.recv_x),

@@ -205,7 +205,7 @@ bool tc_ready();
 
 // parameters of one launch of the tokens-as-A kernels (mmoe_umma_tm.cu)
 struct TmParams {
-  CUtensorMap map_w_routed;        // box 192 rows x 128 K
+  CUtensorMap map_w_routed;        // box 192 rows x 128 K (96 rows for CTA pairs)
   CUtensorMap map_w_shared;
   CUtensorMap map_tok_routed[2];   // boxes of 64 / 128 token rows
   CUtensorMap map_tok_shared[2];
@@ -242,6 +242,6 @@ struct TmParams {
   int has_shared_weights;
 };
 cudaError_t tm_prepare();
-cudaError_t tm_launch(int layer, bool fused, const TmParams& p, cudaStream_t s);
+cudaError_t tm_launch(int layer, bool fused, int ctas, const TmParams& p, cudaStream_t s);   // ctas: 1, or 2 for CTA pairs
 
 }  // namespace mmoe

@@ -25,6 +25,8 @@
 // of the rank the token came from (plain peer stores over NVLink, no TMA from or to peer memory), and `tile_select`
 // restricts a launch to the routed tiles or to the shared expert's tiles planned ahead, so that the shared expert can
 // run while the dispatch is still in flight on another stream.
+#include <type_traits>
+
 #include "mmoe_tc.cuh"
 
 namespace mmoe {
@@ -379,17 +381,21 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
           const int c = i0 >> 5;
           const float wcur = c == 0 ? wv[0] : (c == 1 ? wv[1] : (c == 2 ? wv[2] : wv[3]));
           int my_sf = 0;
-          // branch-free over the 16 columns so that their dependency chains interleave; padding columns compute
-          // garbage that is never stored
+          // branch-free over the 16 columns so that their dependency chains interleave (the fast-math choice is made
+          // once per batch, not per element); padding columns compute garbage that is never stored
+          auto batch = [&](auto fast) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float wt = __shfl_sync(0xffffffffu, wcur, (i0 & 16) + j);
-            const float a = swiglu_act(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp, p.fast_math != 0);
-            const float amax = warp_max_nonneg(fabsf(a));
-            const int sf_exp = ue8m0_exp_of_amax(amax);
-            g[j] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
-            if (lane == j) my_sf = sf_exp;
-          }
+            for (int j = 0; j < 16; ++j) {
+              const float wt = __shfl_sync(0xffffffffu, wcur, (i0 & 16) + j);
+              const float a = swiglu_act_t<decltype(fast)::value>(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp);
+              const float amax = warp_max_nonneg(fabsf(a));
+              const int sf_exp = ue8m0_exp_of_amax(amax);
+              g[j] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
+              if (lane == j) my_sf = sf_exp;
+            }
+          };
+          if (p.fast_math != 0) batch(std::true_type{});
+          else batch(std::false_type{});
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (i0 + j < tile.n_valid) act_col[(int64_t)(i0 + j) * p.inter] = static_cast<uint8_t>(g[j]);
@@ -466,7 +472,7 @@ EncodeTiledFn g_encode = nullptr;
 constexpr int kMaxDevices = 64;
 int g_num_sms[kMaxDevices] = {};   // per device, 0 = mmoe_prepare() has not run there
 int g_tune_stages = 0;             // 0: every stage that fits
-int g_orientation = 0;             // 0: chosen per call, 1: weights-as-A always, 2: tokens-as-A wherever the geometry allows
+int g_orientation = 0;             // 0: chosen per call, 1: weights-as-A, 2: tokens-as-A, 3: tokens-as-A on CTA pairs
 
 int current_device() {
   int dev = -1;
@@ -532,8 +538,10 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
   const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
   TmParams p1{};
   int bad = 0;
-  bad |= make_weight_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride, 192);
-  if (has_shared) bad |= make_weight_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0, 192);
+  const int ctas = c.family == kFamilyTokensAsAPair ? 2 : 1;
+  const uint32_t wbox = 192 / ctas;          // a CTA of a pair stages half of a task's weight rows
+  bad |= make_weight_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride, wbox);
+  if (has_shared) bad |= make_weight_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0, wbox);
   else p1.map_w_shared = p1.map_w_routed;
   const uint32_t kBoxes[2] = {64, 128};
   // a 128-row box may start up to 127 rows before the end of the token matrix; the rows past it are workspace bytes of
@@ -576,8 +584,8 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
   p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
 
   TmParams p2 = p1;
-  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride, 192);
-  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0, 192);
+  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride, wbox);
+  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0, wbox);
   else p2.map_w_shared = p2.map_w_routed;
   for (int b = 0; b < 2; ++b) {
     bad |= make_token_map(&p2.map_tok_routed[b], c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b]);
@@ -606,9 +614,9 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
 
   const int mask = o.layer_mask == 0 ? 3 : o.layer_mask;
   cudaError_t e = cudaSuccess;
-  if (mask & 1) e = tm_launch(1, false, p1, s);
+  if (mask & 1) e = tm_launch(1, false, ctas, p1, s);
   if (e != cudaSuccess) return e;
-  if (mask & 2) e = tm_launch(2, fused, p2, s);
+  if (mask & 2) e = tm_launch(2, fused, ctas, p2, s);
   return e;
 }
 
@@ -693,7 +701,7 @@ cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOp
   const int box = box_rows_of(block_m);
   const bool has_shared = c.geo.num_shared_experts > 0 && w.shared_w13 != nullptr && m > 0;
   const int64_t timeout_ns = (o.timeout_ms > 0 ? (int64_t)o.timeout_ms : 2000) * 1000000ll;
-  if (c.token_major) return launch_experts_tm(c, w, o, m, has_shared, timeout_ns, s);
+  if (c.family != kFamilyWeightsAsA) return launch_experts_tm(c, w, o, m, has_shared, timeout_ns, s);
 
   UmmaParams p1{};
   int bad = 0;

@@ -19,8 +19,23 @@
 //   warp 0     tile producer: per 128-K stage one TMA box of token rows and one of weight rows (packed FP4 expands to
 //              byte containers on the way into shared memory; no cluster multicast)
 //   warp 6     scale producer: per stage one 512-byte chunk of token scales and one or two of weight scales
-//   warp 1     MMA issuer: tcgen05.cp of the scale chunks into TMEM, 4 UMMAs, commit of the stage and of the accumulator
+//   warp 7     scale copier: tcgen05.cp of the stage's chunks into that stage's own TMEM columns, then a commit that
+//              arrives on the stage's `full` barrier
+//   warp 1     MMA issuer: per stage one barrier probe, 4 UMMAs, one commit
 //   warps 2-5  epilogue
+//
+// Every tcgen05 instruction costs its issuing thread about 50 clk, so the one thread that feeds the tensor pipe issues
+// nothing but the UMMAs and the commit (measured: with the three scale copies and a whole-warp barrier probe in the
+// same loop a stage took 510 clk of issue against 384 clk of tensor work).  The scale columns are per pipeline stage
+// (12 of the 128 TMEM columns the two accumulators leave free), so the copier runs ahead of the issuer like the
+// producers do.
+//
+// CTA pairs (kCtas = 2, `tcgen05.mma.cta_group::2`, M = 256): two token tiles of the same expert share one task.  Each
+// CTA stages its own token tile and HALF of the task's weight rows (96), the pair's tensor cores read both halves; the
+// leader CTA's threads issue the scale copies and the UMMAs for both.  Both kernel families are bound by shared-memory
+// bandwidth (about 146 B/clk for TMA fills and operand reads together, measured on both): a single CTA moves 20 KB per
+// UMMA slot of 96 clk, a pair 14 KB per CTA, which is what lets the tensor pipe run at its own rate.  No load uses
+// cluster multicast: every CTA fetches its own boxes, completion crosses the pair as plain mbarrier arrivals.
 //
 // The same roles exist in the reference's kernel (backend/kernel/tma_warps.py, mma_warp.py, epilogue.py).  Persistent
 // CTAs (one per SM) walk the static task list tile-major, so that the CTAs working at the same time share a token tile
@@ -33,27 +48,36 @@ namespace mmoe {
 
 namespace {
 
-constexpr int kTmThreads = 224;
+constexpr int kTmThreads = 256;
 constexpr int kTmN = 192;                          // weight rows of a full task (UMMA N)
-constexpr int kTmRows = 128;                       // token rows of a tile (UMMA M)
-constexpr int kTmABytes = kTmRows * kTileK;        // 16 KB
-constexpr int kTmBBytes = kTmN * kTileK;           // 24 KB of byte containers
-constexpr int kTmSfBytes = 512 + 2 * 512;          // token scale chunk, two weight scale chunks
-constexpr int kTmStageBytes = kTmABytes + kTmBBytes + kTmSfBytes;
-constexpr int kTmStages = (kSmemBudget - 1024) / kTmStageBytes;
-constexpr int kTmSmemBytes = 1024 + kTmStages * kTmStageBytes + 1024;   // control block + stages + alignment slack
-constexpr int kTmAccCols = kTmN;                   // TMEM columns of one accumulator
-constexpr int kTmSfaCol = 2 * kTmAccCols;          // 4 columns: scales of the 128 token rows
-constexpr int kTmSfbCol = kTmSfaCol + 8;           // 8 columns: scales of up to 256 weight rows
-static_assert(kTmStages >= 4 && kTmStages <= 8, "pipeline depth");
-static_assert(kTmSfbCol + 8 <= (int)kTmemCols, "TMEM budget");
-static_assert(kTmSmemBytes <= 227 * 1024, "shared memory budget");
+constexpr int kTmRows = 128;                       // token rows of a tile (UMMA M per CTA)
+constexpr int kTmSfColsPerStage = 12;              // 4: scales of the 128 token rows, 8: scales of up to 256 weight rows
 
-struct TmControl {        // lives at the start of shared memory
-  uint64_t full[8];       // producers -> MMA warp: the stage's copies have landed (one arrival per producer)
-  uint64_t empty[8];      // MMA -> producers: the stage's shared memory may be overwritten
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+template <int kCtas>
+struct TmShape {
+  static constexpr int kBoxN = kTmN / kCtas;                // weight rows one CTA stages
+  static constexpr int kABytes = kTmRows * kTileK;          // 16 KB
+  static constexpr int kBBytes = kBoxN * kTileK;            // 24 KB / 12 KB of byte containers
+  static constexpr int kSfBytes = 512 + 2 * 512;            // token scale chunk, two weight scale chunks
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
+  static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;   // control block + stages + alignment slack
+  static constexpr int kAccCols = kTmN;                     // TMEM columns of one accumulator
+  static constexpr int kSfCol = 2 * kAccCols;               // scale columns of stage s: [kSfCol + 12 s, + 12)
+  static_assert(kStages >= 4, "pipeline depth");
+  static_assert(kSfCol + kStages * kTmSfColsPerStage <= (int)kTmemCols, "TMEM budget");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+struct TmControl {        // lives at the start of shared memory (same layout in both CTAs of a pair)
+  uint64_t tile_full[8];  // tile producer -> scale copier / relay: this CTA's boxes of the stage have landed
+  uint64_t sf_full[8];    // scale producer -> scale copier / relay: this CTA's scale chunks have landed
+  uint64_t pair_ready[8]; // leader only: the peer CTA's boxes and chunks of the stage have landed
+  uint64_t mma_ready[8];  // leader only: scale copier -> MMA issuer: everything of the stage is in place in both CTAs
+  uint64_t empty[8];      // MMA issuer -> producers (of both CTAs): the stage may be overwritten
+  uint64_t tmem_full[2];  // MMA issuer -> epilogue (of both CTAs)
+  uint64_t tmem_empty[2]; // leader only: epilogue warps (of both CTAs) -> MMA issuer
   uint32_t tmem_base;
   volatile int32_t abort_flag;
   // layer 2 with the write-back fused in: slot s < 32 is `ret_recv` of source rank s
@@ -63,35 +87,121 @@ struct TmControl {        // lives at the start of shared memory
 };
 static_assert(sizeof(TmControl) <= 1024, "control block");
 
+// ---------------------------------------------------------------------------------------------------------------
+// cluster / CTA-pair helpers
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <int kCtas>
+__device__ __forceinline__ void tm_commit(uint32_t bar) {
+  if (kCtas == 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  else asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int kCtas>
+__device__ __forceinline__ void tm_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
+  if (kCtas == 1) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+  else asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+}
+template <int kCtas>
+__device__ __forceinline__ void tm_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                       uint32_t accumulate) {
+  if (kCtas == 1) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
 // A task's slice of the expert's stored weight rows.  The rows of an expert are handled as two halves (the two slices
 // of the `localize()` form, or simply the two halves of a plain tensor); a half is cut into blocks of 192 rows, the last
-// one possibly shorter (a multiple of 64).  A short block loads the 192 rows that END at its last row, so that every
-// box lies inside the half, and skips the leading rows through the operand descriptor.
+// one possibly shorter (a multiple of 64).  A CTA stages `n_cols / kCtas` of the block's rows; when that is fewer than
+// its box holds, it loads the box that ENDS at its last row, so that every box lies inside the half, and skips the
+// leading rows through the operand descriptor.
 struct TmBlock {
-  int part, r0, n_cols, shift;   // half, first stored row (within the expert), rows used, rows skipped at the box start
+  int part, r0, n_cols;   // half, first stored row (within the expert), rows used
 };
 __device__ __forceinline__ TmBlock tm_block(int nb, int half, int blocks_per_half) {
   TmBlock b;
   b.part = nb / blocks_per_half;
   const int r_part = (nb - b.part * blocks_per_half) * kTmN;
   b.n_cols = min(kTmN, half - r_part);
-  b.shift = kTmN - b.n_cols;
   b.r0 = b.part * half + r_part;
   return b;
 }
 
-template <int kLayer, bool kFused>
+// Layer-1 epilogue of one scale group: 64 accumulator columns = 32 channels (columns 16b + j hold the gate, 16b + 8 + j
+// the up value of channel 8b + j) -> SwiGLU, x top-k weight, amax, UE8M0 exponent, 32 E4M3 bytes.  The fast-math choice
+// is a template parameter: a per-element branch would serialise the 32 independent dependency chains.
+template <bool kFast>
+__device__ __forceinline__ int tm_l1_group(const uint32_t (&v)[64], float wt, float clamp, uint32_t (&w)[8]) {
+  float a[32];
+  uint32_t amax_bits = 0;
+#pragma unroll
+  for (int b = 0; b < 4; ++b)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float x = swiglu_act_t<kFast>(__uint_as_float(v[16 * b + j]), __uint_as_float(v[16 * b + 8 + j]), wt, clamp);
+      a[8 * b + j] = x;
+      amax_bits = max(amax_bits, __float_as_uint(fabsf(x)));
+    }
+  const int sf_exp = ue8m0_exp_of_amax(__uint_as_float(amax_bits));
+  const float inv = ue8m0_inv(sf_exp);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[4 * c], inv), __fmul_rn(a[4 * c + 1], inv)),
+                                                 __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[4 * c + 2], inv), __fmul_rn(a[4 * c + 3], inv)),
+                                                 __NV_SATFINITE, __NV_E4M3);
+    w[c] = lo | (hi << 16);
+  }
+  return sf_exp;
+}
+
+template <int kLayer, bool kFused, int kCtas>
 __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant__ TmParams p) {
   static_assert(!kFused || kLayer == 2, "only GEMM2 writes rows back");
+  using S = TmShape<kCtas>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);   // the same offset in both CTAs of a pair
   TmControl* ctl = reinterpret_cast<TmControl*>(smem);
   uint8_t* a_base = smem + 1024;
-  uint8_t* b_base = a_base + kTmStages * kTmABytes;
-  uint8_t* sf_base = b_base + kTmStages * kTmBBytes;
+  uint8_t* b_base = a_base + S::kStages * S::kABytes;
+  uint8_t* sf_base = b_base + S::kStages * S::kBBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = kCtas == 2 ? cluster_ctarank() : 0u;      // 0 = leader
+  const bool leader = cta == 0;
+  const int unit = blockIdx.x / kCtas, num_units = gridDim.x / kCtas;   // a unit = one CTA or one CTA pair
   PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
   const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
   const int num_tiles = p.tile_select == 2
@@ -100,17 +210,23 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
   const int half = p.rows_per_expert / 2;
   const int blocks_per_half = (half + kTmN - 1) / kTmN;
   const int n_blocks = 2 * blocks_per_half;
-  const int64_t num_tasks = (int64_t)num_tiles * n_blocks;
+  // a pair plan holds an even number of tiles per expert: tiles 2j and 2j + 1 form pair j
+  const int64_t num_tasks = (int64_t)(num_tiles / kCtas) * n_blocks;
   const int k_stages = p.k_dim / kTileK;
+  // tile record of task `t` for this CTA
+  auto tile_of = [&](int64_t t) -> Tile { return tiles[(t / n_blocks) * kCtas + cta]; };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kTmStages; ++i) {
-      mbar_init(smem_u32(&ctl->full[i]), 2);           // the two producers
+    for (int i = 0; i < S::kStages; ++i) {
+      mbar_init(smem_u32(&ctl->tile_full[i]), 1);
+      mbar_init(smem_u32(&ctl->sf_full[i]), 1);
+      mbar_init(smem_u32(&ctl->pair_ready[i]), 1);
+      mbar_init(smem_u32(&ctl->mma_ready[i]), 1);
       mbar_init(smem_u32(&ctl->empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctl->tmem_full[i]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty[i]), 128);
+      mbar_init(smem_u32(&ctl->tmem_empty[i]), 4 * kCtas);        // one arrival per epilogue warp of the unit
     }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -129,54 +245,62 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
       ctl->rank_off[p.num_ranks] = run;
     }
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {       // the same warp of both CTAs of a pair allocates
+    if (kCtas == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kCtas == 2) cluster_sync_all();       // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
   Waiter waiter{&ctl->abort_flag, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), 20 + kLayer, warp};
-  const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+  const uint32_t tile_full0 = smem_u32(&ctl->tile_full[0]), sf_full0 = smem_u32(&ctl->sf_full[0]);
+  const uint32_t pair_ready0 = smem_u32(&ctl->pair_ready[0]), mma_ready0 = smem_u32(&ctl->mma_ready[0]);
+  const uint32_t empty0 = smem_u32(&ctl->empty[0]);
 
+  // Every role walks the same task list; a one-thread role is a loop that runs at instruction latency, so everything
+  // that does not change inside a task is computed once per task.  The next task's tile record is requested at the top
+  // of a task and consumed at the bottom: its latency hides behind the task instead of stalling the next one.
   if (warp == 0) {
     // --------------------------------------------------------------------------------------------- tile producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       const uint32_t a0 = smem_u32(a_base), b0 = smem_u32(b_base);
       bool ok = true;
-      Tile tile = blockIdx.x < num_tasks ? tiles[blockIdx.x / n_blocks] : Tile{};
-      for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
-        const int tile_idx = static_cast<int>(task / n_blocks);
-        const int nb = static_cast<int>(task - (int64_t)tile_idx * n_blocks);
-        // the next task's tile record is requested now and consumed at the bottom of the loop: its latency hides behind
-        // this task instead of stalling the first stage of the next one
+      Tile tile = unit < num_tasks ? tile_of(unit) : Tile{};
+      for (int64_t task = unit; task < num_tasks && ok; task += num_units) {
+        const int nb = static_cast<int>(task % n_blocks);
         Tile next_tile = tile;
-        if (task + gridDim.x < num_tasks) next_tile = tiles[(task + gridDim.x) / n_blocks];
+        if (task + num_units < num_tasks) next_tile = tile_of(task + num_units);
         const bool shared = tile.expert == kSharedExpert;
         const int e = shared ? 0 : tile.expert;
         const TmBlock blk = tm_block(nb, half, blocks_per_half);
         const bool sliced = !shared && p.routed_sliced != 0;
-        const int box_row = blk.r0 - blk.part * half - blk.shift;          // inside the half: half >= 192
+        // this CTA's rows of the block: [r0 + cta * n_cols / kCtas, + n_cols / kCtas), loaded by the box that ends there
+        const int mine = blk.n_cols / kCtas;
+        const int box_row = blk.r0 - blk.part * half + (int)cta * mine + mine - S::kBoxN;   // >= 0: half > 192 if short
         const int row = sliced ? e * half + box_row : e * p.rows_per_expert + blk.part * half + box_row;
         const int slice = sliced ? blk.part : 0;
         const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
         const int box_sel = tile.n_valid <= 64 ? 0 : 1;
         const CUtensorMap* tmap = shared ? &p.map_tok_shared[box_sel] : &p.map_tok_routed[box_sel];
         // packed FP4 counts its global bytes
-        const uint32_t tx = (box_sel ? kTmRows : 64) * kTileK + (shared ? kTmN * kTileK : kTmN * kTileK / 2);
+        const uint32_t tx = (box_sel ? kTmRows : 64) * kTileK + (shared ? S::kBoxN * kTileK : S::kBoxN * kTileK / 2);
         int k0 = 0;
         for (int kb = 0; kb < k_stages; ++kb, k0 += kTileK) {
           if (!waiter.wait(empty0 + 8 * stage, phase ^ 1u)) { ok = false; break; }
-          const uint32_t bar = full0 + 8 * stage;
+          const uint32_t bar = tile_full0 + 8 * stage;
           mbar_expect_tx(bar, tx);
-          tma_load_3d(b0 + stage * kTmBBytes, wmap, k0, row, slice, bar);
-          tma_load_2d(a0 + stage * kTmABytes, tmap, k0, tile.row0, bar);
-          if (++stage == kTmStages) { stage = 0; phase ^= 1u; }
+          tma_load_3d(b0 + stage * S::kBBytes, wmap, k0, row, slice, bar);
+          tma_load_2d(a0 + stage * S::kABytes, tmap, k0, tile.row0, bar);
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
         }
         tile = next_tile;
       }
@@ -187,14 +311,11 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
       uint32_t stage = 0, phase = 0;
       const uint32_t sf0 = smem_u32(sf_base);
       bool ok = true;
-      Tile tile = blockIdx.x < num_tasks ? tiles[blockIdx.x / n_blocks] : Tile{};
-      for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
-        const int tile_idx = static_cast<int>(task / n_blocks);
-        const int nb = static_cast<int>(task - (int64_t)tile_idx * n_blocks);
-        // the next task's tile record is requested now and consumed at the bottom of the loop: its latency hides behind
-        // this task instead of stalling the first stage of the next one
+      Tile tile = unit < num_tasks ? tile_of(unit) : Tile{};
+      for (int64_t task = unit; task < num_tasks && ok; task += num_units) {
+        const int nb = static_cast<int>(task % n_blocks);
         Tile next_tile = tile;
-        if (task + gridDim.x < num_tasks) next_tile = tiles[(task + gridDim.x) / n_blocks];
+        if (task + num_units < num_tasks) next_tile = tile_of(task + num_units);
         const bool shared = tile.expert == kSharedExpert;
         const int e = shared ? 0 : tile.expert;
         const TmBlock blk = tm_block(nb, half, blocks_per_half);
@@ -204,81 +325,121 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
         const int64_t tsf_rows = shared ? p.tsf_rows_shared : p.tsf_rows_routed;
         const int32_t* tsf = (shared ? p.tsf_shared : p.tsf_routed) + (int64_t)tile.sf_chunk * kChunkRows;
         for (int kb = 0; kb < k_stages; ++kb, wsf += p.rows_per_expert, tsf += tsf_rows) {
+          // the stage's previous UMMAs have retired: its shared memory AND its scale columns in TMEM are free
           if (!waiter.wait(empty0 + 8 * stage, phase ^ 1u)) { ok = false; break; }
-          const uint32_t bar = full0 + 8 * stage;
-          const uint32_t dst = sf0 + stage * kTmSfBytes;
+          const uint32_t bar = sf_full0 + 8 * stage;
+          const uint32_t dst = sf0 + stage * S::kSfBytes;
           mbar_expect_tx(bar, 512u + sfb_bytes);
-          bulk_load(dst + 512, wsf, sfb_bytes, bar);
+          bulk_load(dst + 512, wsf, sfb_bytes, bar);          // every CTA of a pair holds the scales of all the block's rows
           bulk_load(dst, tsf, 512, bar);
-          if (++stage == kTmStages) { stage = 0; phase ^= 1u; }
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
         }
         tile = next_tile;
       }
     }
+  } else if (warp == 7) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      if (leader) {
+        // ----------------------------------------------------------------------------------------- scale copier
+        const uint64_t sf_hi = desc_hi_sf(128);
+        const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
+        for (int64_t task = unit; task < num_tasks && ok; task += num_units) {
+          const int nb = static_cast<int>(task % n_blocks);
+          const TmBlock blk = tm_block(nb, half, blocks_per_half);
+          const bool two_chunks = (blk.r0 % kChunkRows) + blk.n_cols > kChunkRows;
+          for (int kb = 0; kb < k_stages; ++kb) {
+            if (!waiter.wait(sf_full0 + 8 * stage, phase)) { ok = false; break; }
+            if (!waiter.wait(tile_full0 + 8 * stage, phase)) { ok = false; break; }
+            if (kCtas == 2 && !waiter.wait(pair_ready0 + 8 * stage, phase)) { ok = false; break; }
+            const uint32_t sf_lo = sf_lo0 + stage * (S::kSfBytes >> 4);
+            const uint32_t col = tmem_base + S::kSfCol + stage * kTmSfColsPerStage;
+            // cta_group::2: every CTA of the pair copies from its own shared memory into its own tensor memory
+            tm_cp_sf<kCtas>(col, sf_hi | sf_lo);                                   // token scales
+            tm_cp_sf<kCtas>(col + 4, sf_hi | (sf_lo + 32));                        // weight scales, first chunk
+            if (two_chunks) tm_cp_sf<kCtas>(col + 8, sf_hi | (sf_lo + 64));
+            tm_commit<kCtas>(mma_ready0 + 8 * stage);                              // arrives when the copies have completed
+            if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+      } else {
+        // ----------------------------------------------------------------------------------------- relay (peer CTA)
+        // tells the leader that this CTA's boxes and scale chunks of the stage have landed
+        const uint32_t remote0 = map_to_cta(pair_ready0, 0);
+        for (int64_t task = unit; task < num_tasks && ok; task += num_units) {
+          for (int kb = 0; kb < k_stages; ++kb) {
+            if (!waiter.wait(sf_full0 + 8 * stage, phase)) { ok = false; break; }
+            if (!waiter.wait(tile_full0 + 8 * stage, phase)) { ok = false; break; }
+            mbar_arrive_cluster_relaxed(remote0 + 8 * stage);
+            if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
   } else if (warp == 1) {
     // --------------------------------------------------------------------------------------------- MMA issuer
-    // The whole warp walks the loop so that its state stays warp-uniform; one elected lane issues.
-    uint32_t stage = 0, phase = 0, it = 0;
-    bool ok = true;
-    const uint64_t sw128_hi = desc_hi_sw128();
-    const uint64_t sf_hi = desc_hi_sf(128);
-    const uint32_t a_lo0 = (smem_u32(a_base) & 0x3FFFFu) >> 4;
-    const uint32_t b_lo0 = (smem_u32(b_base) & 0x3FFFFu) >> 4;
-    const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
-    Tile tile = blockIdx.x < num_tasks ? tiles[blockIdx.x / n_blocks] : Tile{};
-    for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
-      const int tile_idx = static_cast<int>(task / n_blocks);
-      const int nb = static_cast<int>(task - (int64_t)tile_idx * n_blocks);
-      Tile next_tile = tile;
-      if (task + gridDim.x < num_tasks) next_tile = tiles[(task + gridDim.x) / n_blocks];
-      const bool shared = tile.expert == kSharedExpert;
-      const TmBlock blk = tm_block(nb, half, blocks_per_half);
-      const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
-      if (!waiter.wait_warp(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t idesc0 = make_idesc(0u, shared ? 0u : 5u, static_cast<uint32_t>(blk.n_cols), 0);
-      const uint32_t d = tmem_base + acc_stage * kTmAccCols;
-      const uint32_t sfa = tmem_base + kTmSfaCol + tile.sf_col;
-      const uint32_t sfb_tm = tmem_base + kTmSfbCol;
-      const uint32_t sfb = sfb_tm + (blk.r0 % kChunkRows) / 32;
-      const bool two_chunks = (blk.r0 % kChunkRows) + blk.n_cols > kChunkRows;
-      const uint32_t b_skip = static_cast<uint32_t>(blk.shift * kTileK) >> 4;   // whole 8-row swizzle groups
-      for (int kb = 0; kb < k_stages; ++kb) {
-        if (!waiter.wait_warp(full0 + 8 * stage, phase)) { ok = false; break; }
-        if (elect_one()) {
-          const uint32_t a_lo = a_lo0 + stage * (kTmABytes >> 4);
-          const uint32_t b_lo = b_lo0 + stage * (kTmBBytes >> 4) + b_skip;
-          const uint32_t sf_lo = sf_lo0 + stage * (kTmSfBytes >> 4);
-          tc_cp_sf(tmem_base + kTmSfaCol, sf_hi | sf_lo);
-          tc_cp_sf(sfb_tm, sf_hi | (sf_lo + 32));
-          if (two_chunks) tc_cp_sf(sfb_tm + 4, sf_hi | (sf_lo + 64));
+    if (lane == 0 && leader) {
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      const uint64_t sw128_hi = desc_hi_sw128();
+      const uint32_t a_lo0 = (smem_u32(a_base) & 0x3FFFFu) >> 4;
+      const uint32_t b_lo0 = (smem_u32(b_base) & 0x3FFFFu) >> 4;
+      const uint32_t peer_empty0 = kCtas == 2 ? map_to_cta(empty0, 1) : 0u;
+      const uint32_t peer_tmem_full0 = kCtas == 2 ? map_to_cta(smem_u32(&ctl->tmem_full[0]), 1) : 0u;
+      Tile tile = unit < num_tasks ? tile_of(unit) : Tile{};
+      for (int64_t task = unit; task < num_tasks && ok; task += num_units, ++it) {
+        const int nb = static_cast<int>(task % n_blocks);
+        Tile next_tile = tile;
+        if (task + num_units < num_tasks) next_tile = tile_of(task + num_units);
+        const bool shared = tile.expert == kSharedExpert;
+        const TmBlock blk = tm_block(nb, half, blocks_per_half);
+        const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
+        if (!waiter.wait(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
+        tc_fence_after();
+        // M = 128 per CTA (256 over a pair); idesc field [24,29) = M >> 4
+        const uint32_t idesc0 = make_idesc(0u, shared ? 0u : 5u, static_cast<uint32_t>(blk.n_cols), 0) +
+                                (kCtas == 2 ? ((128u >> 4) << 24) : 0u);
+        const uint32_t d = tmem_base + acc_stage * S::kAccCols;
+        const uint32_t sfa0 = tmem_base + S::kSfCol + tile.sf_col;
+        const uint32_t sfb0 = tmem_base + S::kSfCol + 4 + (blk.r0 % kChunkRows) / 32;
+        // rows skipped at the start of this CTA's box (whole 8-row swizzle groups); the same in both CTAs
+        const uint32_t b_skip = static_cast<uint32_t>((S::kBoxN - blk.n_cols / kCtas) * kTileK) >> 4;
+        for (int kb = 0; kb < k_stages; ++kb) {
+          if (!waiter.wait(mma_ready0 + 8 * stage, phase)) { ok = false; break; }
+          const uint32_t a_lo = a_lo0 + stage * (S::kABytes >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (S::kBBytes >> 4) + b_skip;
+          const uint32_t sfa = sfa0 + stage * kTmSfColsPerStage, sfb = sfb0 + stage * kTmSfColsPerStage;
 #pragma unroll
           for (int k = 0; k < kTileK / 32; ++k)
-            tc_mma(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
-                   idesc0 + k * ((1u << 4) | (1u << 29)),                   // scale byte k of both operands
-                   sfa, sfb, (kb | k) != 0 ? 1u : 0u);
-          tc_commit(empty0 + 8 * stage);              // shared memory of this stage is free once these MMAs retire
+            tm_mma<kCtas>(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
+                          idesc0 + k * ((1u << 4) | (1u << 29)),            // scale byte k of both operands
+                          sfa, sfb, (kb | k) != 0 ? 1u : 0u);
+          // the stage is free in every CTA of the unit once these UMMAs retire
+          tm_commit<kCtas>(empty0 + 8 * stage);
+          if (kCtas == 2) tm_commit<kCtas>(peer_empty0 + 8 * stage);
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
         }
-        __syncwarp();
-        if (++stage == kTmStages) { stage = 0; phase ^= 1u; }
+        if (ok) {
+          tm_commit<kCtas>(smem_u32(&ctl->tmem_full[acc_stage]));
+          if (kCtas == 2) tm_commit<kCtas>(peer_tmem_full0 + 8 * acc_stage);
+        }
+        tile = next_tile;
       }
-      if (ok && elect_one()) tc_commit(smem_u32(&ctl->tmem_full[acc_stage]));
-      __syncwarp();
-      tile = next_tile;
     }
   } else {
     // --------------------------------------------------------------------------------------------- epilogue
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
     const int i = q * 32 + lane;                  // token row of the tile this thread owns
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t tmem_empty_leader0 = kCtas == 2 ? map_to_cta(smem_u32(&ctl->tmem_empty[0]), 0) : smem_u32(&ctl->tmem_empty[0]);
     uint32_t it = 0;
     bool ok = true;
-    Tile tile = blockIdx.x < num_tasks ? tiles[blockIdx.x / n_blocks] : Tile{};
-    for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
-      const int tile_idx = static_cast<int>(task / n_blocks);
-      const int nb = static_cast<int>(task - (int64_t)tile_idx * n_blocks);
+    Tile tile = unit < num_tasks ? tile_of(unit) : Tile{};
+    for (int64_t task = unit; task < num_tasks && ok; task += num_units, ++it) {
+      const int nb = static_cast<int>(task % n_blocks);
       Tile next_tile = tile;
-      if (task + gridDim.x < num_tasks) next_tile = tiles[(task + gridDim.x) / n_blocks];
+      if (task + num_units < num_tasks) next_tile = tile_of(task + num_units);
       const bool shared = tile.expert == kSharedExpert;
       const TmBlock blk = tm_block(nb, half, blocks_per_half);
       const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
@@ -286,60 +447,39 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
       const int64_t row = (int64_t)tile.row0 + i;
       // per-token side data, fetched before the accumulator is awaited
       float wt = 1.0f;
-      __nv_bfloat16* out_row = nullptr;
+      __nv_bfloat16* out = nullptr;
       if (kLayer == 1) {
         if (!shared && live) wt = __ldg(p.pool_w + row);
       } else if (live) {
         if (shared) {
-          out_row = p.shared_out + row * p.hidden;
+          out = p.shared_out + row * p.hidden;
         } else if (!kFused) {
-          out_row = p.ret + (int64_t)__ldg(p.pool_dst + row) * p.hidden;
+          out = p.ret + (int64_t)__ldg(p.pool_dst + row) * p.hidden;
         } else {
           const int r = __ldg(p.pool_dst + row);          // receive-order row -> source rank and its send position
           int sr = 0;
           while (sr + 1 < p.num_ranks && r >= ctl->rank_off[sr + 1]) ++sr;
-          out_row = ctl->out_base[sr] + (int64_t)(ctl->home_base[sr] + r - ctl->rank_off[sr]) * p.hidden;
+          out = ctl->out_base[sr] + (int64_t)(ctl->home_base[sr] + r - ctl->rank_off[sr]) * p.hidden;
         }
+        out += blk.r0;
       }
       if (!waiter.wait_warp(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t d0 = tmem_base + lane_sel + acc_stage * kTmAccCols;
+      const uint32_t d0 = tmem_base + lane_sel + acc_stage * S::kAccCols;
       if (kLayer == 1) {
-        // 64 stored rows = 32 channels = one scale group: columns 16b + j hold the gate, 16b + 8 + j the up value of
-        // channel 8b + j
         uint8_t* act = (shared ? p.act_shared : p.act_routed) + row * p.inter + (blk.r0 >> 1);
         uint8_t* act_sf = shared ? p.act_sf_shared : p.act_sf_routed;
         const int64_t sf_rows = shared ? p.act_sf_rows_shared : p.act_sf_rows_routed;
         const int64_t sf_pos = (int64_t)tile.sf_chunk * kChunkRows + chunk_pos(tile.sf_col * 32 + i);
         const int grp0 = blk.r0 >> 6;
+        const bool fast = p.fast_math != 0;
 #pragma unroll 1
         for (int g = 0; g < (blk.n_cols >> 6); ++g) {
-          uint32_t v[64];
+          uint32_t v[64], w[8];
           tc_ld32(d0 + 64 * g, v);
           tc_ld32(d0 + 64 * g + 32, v + 32);
           tc_ld_wait();
-          float a[32];
-          uint32_t amax_bits = 0;
-#pragma unroll
-          for (int b = 0; b < 4; ++b)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float x = swiglu_act(__uint_as_float(v[16 * b + j]), __uint_as_float(v[16 * b + 8 + j]), wt, p.clamp,
-                                         p.fast_math != 0);
-              a[8 * b + j] = x;
-              amax_bits = max(amax_bits, __float_as_uint(fabsf(x)));
-            }
-          const int sf_exp = ue8m0_exp_of_amax(__uint_as_float(amax_bits));
-          const float inv = ue8m0_inv(sf_exp);
-          uint32_t w[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[4 * c], inv), __fmul_rn(a[4 * c + 1], inv)),
-                                                         __NV_SATFINITE, __NV_E4M3);
-            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[4 * c + 2], inv), __fmul_rn(a[4 * c + 3], inv)),
-                                                         __NV_SATFINITE, __NV_E4M3);
-            w[c] = lo | (hi << 16);
-          }
+          const int sf_exp = fast ? tm_l1_group<true>(v, wt, p.clamp, w) : tm_l1_group<false>(v, wt, p.clamp, w);
           if (live) {
             uint4* dst = reinterpret_cast<uint4*>(act + 32 * g);
             dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -349,27 +489,32 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
           }
         }
       } else {
-        __nv_bfloat16* out = live ? out_row + blk.r0 : nullptr;
 #pragma unroll 1
-        for (int c0 = 0; c0 < blk.n_cols; c0 += 32) {
-          uint32_t v[32];
+        for (int c0 = 0; c0 < blk.n_cols; c0 += 64) {
+          uint32_t v[64];
           tc_ld32(d0 + c0, v);
+          tc_ld32(d0 + c0 + 32, v + 32);
           tc_ld_wait();
-          uint32_t w[16];
+          uint32_t w[32];
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < 32; ++c) {
             const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(v[2 * c]), __uint_as_float(v[2 * c + 1]));
             w[c] = *reinterpret_cast<const uint32_t*>(&pr);
           }
           if (live) {
             uint4* dst = reinterpret_cast<uint4*>(out + c0);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) dst[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+            for (int c = 0; c < 8; ++c) dst[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
           }
         }
       }
+      // the accumulator is drained: one arrival per warp on the leader's barrier
       tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->tmem_empty[acc_stage]));
+      __syncwarp();
+      if (lane == 0) {
+        if (kCtas == 2) mbar_arrive_cluster(tmem_empty_leader0 + 8 * acc_stage);
+        else mbar_arrive(tmem_empty_leader0 + 8 * acc_stage);
+      }
       tile = next_tile;
     }
   }
@@ -383,28 +528,62 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  if (kCtas == 2) cluster_sync_all();       // no CTA leaves while its peer may still arrive on its barriers
   tc_fence_after();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (kCtas == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+}
+
+template <int kLayer, bool kFused, int kCtas>
+cudaError_t tm_launch_one(const TmParams& p, int grid, cudaStream_t s) {
+  using S = TmShape<kCtas>;
+  if (kCtas == 1) {
+    tm_kernel<kLayer, kFused, 1><<<grid, kTmThreads, S::kSmemBytes, s>>>(p);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid & ~1);
+  cfg.blockDim = dim3(kTmThreads);
+  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, tm_kernel<kLayer, kFused, kCtas>, p);
+}
+
+template <int kCtas>
+cudaError_t tm_prepare_ctas() {
+  const int bytes = TmShape<kCtas>::kSmemBytes;
+  cudaError_t e = cudaFuncSetAttribute(tm_kernel<1, false, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, false, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, true, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e;
 }
 
 }  // namespace
 
 cudaError_t tm_prepare() {
-  cudaError_t e = cudaFuncSetAttribute(tm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmSmemBytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmSmemBytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmSmemBytes);
+  cudaError_t e = tm_prepare_ctas<1>();
+  if (e == cudaSuccess) e = tm_prepare_ctas<2>();
   return e;
 }
 
-cudaError_t tm_launch(int layer, bool fused, const TmParams& p, cudaStream_t s) {
+cudaError_t tm_launch(int layer, bool fused, int ctas, const TmParams& p, cudaStream_t s) {
   const int grid = tc_num_sms();
   if (grid <= 0) return cudaErrorNotReady;
-  if (layer == 1) tm_kernel<1, false><<<grid, kTmThreads, kTmSmemBytes, s>>>(p);
-  else if (fused) tm_kernel<2, true><<<grid, kTmThreads, kTmSmemBytes, s>>>(p);
-  else tm_kernel<2, false><<<grid, kTmThreads, kTmSmemBytes, s>>>(p);
-  return cudaGetLastError();
+  if (ctas == 2) {
+    if (layer == 1) return tm_launch_one<1, false, 2>(p, grid, s);
+    return fused ? tm_launch_one<2, true, 2>(p, grid, s) : tm_launch_one<2, false, 2>(p, grid, s);
+  }
+  if (layer == 1) return tm_launch_one<1, false, 1>(p, grid, s);
+  return fused ? tm_launch_one<2, true, 1>(p, grid, s) : tm_launch_one<2, false, 1>(p, grid, s);
 }
 
 }  // namespace mmoe
