@@ -233,8 +233,8 @@ int mmoe_read_status(const MmoeGeometry* geo, void* workspace, int32_t* words8, 
  * cap).  `orientation`: 0 = chosen per call (weights-as-A kernels below about 80 expected rows per expert, tokens-as-A
  * kernels from there, and for the shared expert of a call with more than 128 tokens), 1 = weights-as-A always, 2 =
  * tokens-as-A wherever the geometry allows (intermediate >= 192, hidden >= 384), 3 = tokens-as-A on CTA pairs
- * (`tcgen05.mma.cta_group::2`) wherever the geometry and BLOCK_M (>= 128) allow; never chosen automatically, see the
- * measurements in the design notes.  Every rank and every step of a call (planning, GEMM launches) must see the same
+ * (`tcgen05.mma.cta_group::2`) wherever the geometry and BLOCK_M (>= 128) allow; never chosen automatically: measured
+ * on B200 it is slower than single CTAs at 120 to 480 rows per expert.  Every rank and every step of a call (planning, GEMM launches) must see the same
  * setting. */
 int mmoe_set_tuning(int32_t max_stages, int32_t orientation);
 

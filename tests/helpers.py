@@ -96,3 +96,55 @@ def run_layer(layer: Layer, hidden, ids, w, *, t_max: int = 1920, clamp=10.0, fa
 def oracle_layer(layer: Layer, hidden, ids, w, clamp=10.0, pad=None):
     return O.moe_layer([hidden], [ids], [w], layer.experts, layer.shared, clamp,
                        None if pad is None else [pad])[0]
+
+
+def synthetic_expert(syn, e: int) -> O.ExpertWeights:
+    """Physical expert ``e`` of a :class:`vllm_plugin_b200.testing.SyntheticLayer` in the oracle's (untransformed) format."""
+    w13, s13, w2, s2 = syn.raw
+    return O.ExpertWeights(w13[e].cpu(), s13[e].cpu(), w2[e].cpu(), s2[e].cpu())
+
+
+def synthetic_shared(syn) -> Optional[O.ExpertWeights]:
+    if syn.shared_raw is None:
+        return None
+    q13, e13, q2, e2 = syn.shared_raw
+    return O.ExpertWeights(q13.cpu(), e13.cpu(), q2.cpu(), e2.cpu(), fp8=True)
+
+
+def oracle_token_sample(hidden, ids, w, sample, expert_of, shared: Optional[O.ExpertWeights], clamp=10.0):
+    """Oracle output of the tokens ``sample`` (indices) of one call, dequantising ONE expert at a time (``expert_of(e)``
+    returns its :class:`ExpertWeights`), so that a call over hundreds of resident experts can be checked: only the
+    experts the sampled tokens hit are touched.  A token's output does not depend on the rest of the call."""
+    sample = torch.as_tensor(sample, dtype=torch.long)
+    hid = hidden.cpu()[sample]
+    q, sf, ids_s, w_s, _ = O.stage_inputs(hid, ids.cpu()[sample], w.cpu()[sample], None)
+    n, k = ids_s.shape
+    slot_out = torch.zeros((k, n, hid.shape[1]), dtype=torch.bfloat16)
+    sf_bytes = O.unpack_sf_words(sf)
+    for e in torch.unique(ids_s[ids_s >= 0]).tolist():
+        tok, slot = torch.nonzero(ids_s == e, as_tuple=True)
+        w13, w2 = expert_of(e).dequant()
+        slot_out[slot, tok] = O.expert_forward(q[tok], sf_bytes[tok], w_s[tok, slot], w13, w2, clamp)
+    sh = None
+    if shared is not None:
+        s13, s2 = shared.dequant()
+        sh = O.expert_forward(q, sf_bytes, torch.ones(n, dtype=torch.float32), s13, s2, clamp)
+    return O.combine(slot_out, ids_s, sh)
+
+
+def strict_metrics(y, ref) -> dict:
+    """rel-L2, the strict max_abs and the number of elements above 2e-2 (the tolerance tests additionally allow one BF16
+    ulp of the reference where that ulp exceeds 2e-2)."""
+    a, b = y.float().cpu(), ref.float().cpu()
+    d = (a - b).abs()
+    return {"rel_l2": float((a - b).norm() / b.norm().clamp(min=1e-30)), "max_abs_strict": float(d.max()) if d.numel() else 0.0,
+            "n_over_2e-2": int((d > 2e-2).sum()), "n": int(d.numel()), "max_abs_ref": float(b.abs().max()) if b.numel() else 0.0}
+
+
+def log_parity(name: str, metrics: dict) -> None:
+    """Append the metrics of a parity case to the file named by MMOE_PARITY_LOG (when set), for the measurement notes."""
+    path = os.environ.get("MMOE_PARITY_LOG")
+    if path:
+        import json
+        with open(path, "a") as f:
+            f.write(json.dumps({"case": name, **metrics}) + "\n")

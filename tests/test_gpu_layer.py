@@ -165,7 +165,9 @@ def test_reference_cpu_configuration():
     ids, w = O.make_routing(128, 32, 6, 0)
     y, buf = H.run_layer(layer, hid, ids, w)
     assert buf.plan_tables()[0]["block_m"] == 32
-    assert_parity(y, H.oracle_layer(layer, hid, ids, w), "config 0")
+    ref = H.oracle_layer(layer, hid, ids, w)
+    H.log_parity("config 0: E=32 M=128", H.strict_metrics(y, ref))
+    assert_parity(y, ref, "config 0")
 
 
 def test_full_size_engines_agree_and_permutation_invariance():
