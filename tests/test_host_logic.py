@@ -159,3 +159,27 @@ def test_import_is_light():
             "bad = [m for m in ('torch', 'vllm', 'triton') if m in sys.modules]; assert not bad, bad" % ROOT)
     env = {k: v for k, v in os.environ.items() if k != "VLLM_PLUGINS"}
     subprocess.run([sys.executable, "-c", code], check=True, env=env)
+
+
+def test_admission_gate_and_library_agree_on_the_kernel_limits():
+    """Whatever the Python gate admits with ``allow_unvalidated=True`` the C library must lay out, and what the library
+    refuses the gate must refuse (the gate may be stricter only where the engine-facing contract is: none here)."""
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend import _native
+    lib = _native.load()
+    cases = []
+    for ranks in (1, 2, 3, 8, 32, 33):
+        for experts in (8, 48, 384, 392, 2048, 2056, 16416):
+            for topk in (1, 6, 31, 32):
+                for hidden, inter in ((5120, 2304), (512, 256), (384, 128), (256, 192), (1024, 64)):
+                    cases.append((ranks, experts, 1920, topk, hidden, inter, 1))
+    agree = 0
+    for ranks, experts, tokens, topk, hidden, inter, shared in cases:
+        reason = api.get_unsupported_reason_for_mega_moe(ranks, experts, tokens, topk, hidden, inter, shared,
+                                                         allow_unvalidated=True)
+        geo = _native.MmoeGeometry(ranks, 0, experts, topk, hidden, inter, shared, 1920)
+        lay = _native.MmoeLayout()
+        code = lib.mmoe_layout(ctypes.byref(geo), ctypes.byref(lay))
+        assert (reason is None) == (code == _native.MMOE_OK), (ranks, experts, topk, hidden, inter, reason, code)
+        agree += 1
+    assert agree == len(cases)

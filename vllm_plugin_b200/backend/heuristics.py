@@ -119,65 +119,114 @@ def get_validated_ep_geometries():
     return dict(VALIDATED_EP_GEOMETRIES)
 
 
-def _structural_reason(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-                       num_shared_experts) -> Optional[str]:
-    """Shape rules of the sm_100a kernels (what replaces the reference's per-variant SM107 configuration derivation)."""
-    if num_experts % num_ranks != 0:
-        return f"num_experts={num_experts} is not divisible by num_ranks={num_ranks}"
-    if hidden % TILE_K != 0 or hidden % TILE_ROWS != 0:
-        return f"hidden={hidden} must be a multiple of {TILE_K}"
-    if intermediate_hidden % TILE_K != 0 or intermediate_hidden % TILE_ROWS != 0:
-        return f"intermediate_hidden={intermediate_hidden} must be a multiple of {TILE_K}"
-    if hidden % 256 != 0:
-        return f"hidden={hidden} must be a multiple of 256 (combine vector width)"
-    if num_topk > 31:
-        return f"num_topk={num_topk} exceeds the combine slot mask (31)"
-    t = align(num_max_tokens_per_rank, TOKEN_ALIGNMENT)
-    if t * num_ranks * min(num_topk, num_experts // num_ranks) >= 2 ** 31:
+# ---- the gate as a list of rules, each returning a reason or None; the first reason wins ---------------------------------
+class _Ask:
+    """One admission question with every size coerced to ``int`` (a non-integer size is itself a reason to refuse)."""
+
+    __slots__ = ("ranks", "experts", "tokens", "topk", "hidden", "inter", "shared", "mma", "act", "sms", "fast", "die_shared",
+                 "any_geometry")
+
+    def __init__(self, ranks, experts, tokens, topk, hidden, inter, shared, mma, act, sms, fast, die_shared, any_geometry):
+        sizes = dict(num_ranks=ranks, num_experts=experts, num_max_tokens_per_rank=tokens, num_topk=topk, hidden=hidden,
+                     intermediate_hidden=inter, num_shared_experts=shared)
+        for name, value in sizes.items():
+            if isinstance(value, bool) or not isinstance(value, int):
+                raise TypeError(f"{name}={value!r} is not an integer")
+        self.ranks, self.experts, self.tokens, self.topk = ranks, experts, tokens, topk
+        self.hidden, self.inter, self.shared = hidden, inter, shared
+        self.mma, self.act, self.sms, self.fast = mma, act, sms, fast
+        self.die_shared, self.any_geometry = die_shared, any_geometry
+
+    @property
+    def shape_key(self) -> Tuple[int, int, int]:
+        return (self.hidden, self.inter, self.topk)
+
+    def describe(self) -> str:
+        return (f"geometry (hidden={self.hidden}, intermediate_hidden={self.inter}, num_experts={self.experts}, "
+                f"top-k={self.topk})")
+
+
+def _rule_options(q: _Ask) -> Optional[str]:
+    if q.mma != "fp8xfp4":
+        return f"mma_type={q.mma!r} is not supported (only 'fp8xfp4')"
+    if q.act != "swiglu":
+        return f"activation={q.act!r} is not supported (only 'swiglu')"
+    if q.fast not in (True, False, 0, 1):
+        return f"fast_math={q.fast!r} is not supported"
+    if q.die_shared:
+        return "die-local shared-expert weights are not supported (B200 exposes one memory locality domain)"
+    if q.sms is not None and q.sms < 1:
+        return f"num_sms={q.sms} must be positive"
+    return None
+
+
+def _rule_ranges(q: _Ask) -> Optional[str]:
+    if not 0 <= q.shared <= MAX_SHARED_EXPERTS:
+        return f"num_shared_experts={q.shared} is outside the supported range [0, {MAX_SHARED_EXPERTS}]"
+    if not 1 <= q.ranks <= MAX_RANKS:
+        return f"num_ranks={q.ranks} is outside the supported range [1, {MAX_RANKS}]"
+    positive = (("num_experts", q.experts), ("num_topk", q.topk), ("hidden", q.hidden), ("intermediate_hidden", q.inter),
+                ("num_max_tokens_per_rank", q.tokens))
+    bad = [f"{name}={value}" for name, value in positive if value < 1]
+    return f"{bad[0]} must be positive" if bad else None
+
+
+def _listed(q: _Ask) -> Tuple[bool, bool]:
+    """(the (experts, ranks) pair is listed exactly, the expert count is listed for this shape)."""
+    exact = (q.experts, q.ranks) in VALIDATED_EP_GEOMETRIES.get(q.shape_key, ((), ""))[0]
+    general = q.experts in VALIDATED_GEOMETRIES.get(q.shape_key, ((), ""))[0]
+    return exact, general
+
+
+def _tables_as_text() -> str:
+    general = "; ".join(f"hidden={h}, intermediate_hidden={i}, top-k={k}, num_experts in {list(es)}"
+                        for (h, i, k), (es, _) in VALIDATED_GEOMETRIES.items())
+    exact = "; ".join(f"hidden={h}, intermediate_hidden={i}, top-k={k}, (num_experts, EP size) in {list(ps)}"
+                      for (h, i, k), (ps, _) in VALIDATED_EP_GEOMETRIES.items())
+    return f"validated: {general}; exact pairs: {exact}"
+
+
+def _rule_validated(q: _Ask) -> Optional[str]:
+    """The geometry list is the reference plugin's (geometries its authors ran on their GPUs); on B200 this backend has
+    run the listed shapes at EP 1, 2, 4 and 8.  ``allow_unvalidated`` skips the list, never the kernel limits."""
+    if q.any_geometry:
+        return None
+    exact, general = _listed(q)
+    if exact:
+        return None
+    if not general:
+        return f"{q.describe()} has not been validated on GPUs with {q.ranks} ranks ({_tables_as_text()})"
+    per_rank, rest = divmod(q.experts, q.ranks)
+    if rest == 0 and per_rank < MIN_VALIDATED_EXPERTS_PER_RANK:
+        return (f"{q.describe()} has not been validated on GPUs with {per_rank} experts per rank "
+                f"(the smallest experts-per-rank that has run is {MIN_VALIDATED_EXPERTS_PER_RANK})")
+    return None
+
+
+#: limits the C library enforces on a geometry (``check_geometry`` behind ``mmoe_layout``); kept equal by a test
+MAX_EXPERTS = 2048
+MAX_EXPERTS_PER_RANK = 512
+MAX_TOPK = 31
+
+
+def _rule_kernel_limits(q: _Ask) -> Optional[str]:
+    if q.experts % q.ranks:
+        return f"num_experts={q.experts} is not divisible by num_ranks={q.ranks}"
+    if q.experts > MAX_EXPERTS or q.experts // q.ranks > MAX_EXPERTS_PER_RANK:
+        return f"num_experts={q.experts} exceeds {MAX_EXPERTS} (or {MAX_EXPERTS_PER_RANK} per rank)"
+    if q.topk > MAX_TOPK:
+        return f"num_topk={q.topk} exceeds the combine slot mask ({MAX_TOPK})"
+    if q.hidden % 256:
+        return f"hidden={q.hidden} must be a multiple of 256 (two {TILE_ROWS}-row weight tiles per task, combine vector width)"
+    if q.inter % TILE_K:
+        return f"intermediate_hidden={q.inter} must be a multiple of {TILE_K}"
+    rows = align(q.tokens, TOKEN_ALIGNMENT) * q.ranks * min(q.topk, q.experts // q.ranks)
+    if rows >= 2 ** 31:
         return "token pool exceeds 32-bit row indices"
     return None
 
 
-def _unsupported_reason(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-                        num_shared_experts, mma_type, activation, *, num_sms, fast_math, localized_shared_weights,
-                        allow_unvalidated) -> Optional[str]:
-    if mma_type != "fp8xfp4":
-        return f"mma_type={mma_type!r} is not supported (only 'fp8xfp4')"
-    if activation != "swiglu":
-        return f"activation={activation!r} is not supported (only 'swiglu')"
-    if bool(fast_math) not in (True, False):
-        return f"fast_math={fast_math!r} is not supported"
-    if localized_shared_weights:
-        return "die-local shared-expert weights are not supported (B200 exposes one memory locality domain)"
-    if not 0 <= num_shared_experts <= MAX_SHARED_EXPERTS:
-        return f"num_shared_experts={num_shared_experts} is outside the supported range [0, {MAX_SHARED_EXPERTS}]"
-    if not 1 <= num_ranks <= MAX_RANKS:
-        return f"num_ranks={num_ranks} is outside the supported range [1, {MAX_RANKS}]"
-    for name, value in (("num_experts", num_experts), ("num_topk", num_topk), ("hidden", hidden),
-                        ("intermediate_hidden", intermediate_hidden),
-                        ("num_max_tokens_per_rank", num_max_tokens_per_rank)):
-        if value < 1:
-            return f"{name}={value} must be positive"
-    if num_sms is not None and num_sms < 1:
-        return f"num_sms={num_sms} must be positive"
-    key = (hidden, intermediate_hidden, num_topk)
-    exact_pairs = VALIDATED_EP_GEOMETRIES.get(key, ((), ""))[0]
-    if not allow_unvalidated and (num_experts, num_ranks) not in exact_pairs:
-        entry = VALIDATED_GEOMETRIES.get(key)
-        if entry is None or num_experts not in entry[0]:
-            known = "; ".join(f"hidden={k[0]}, intermediate_hidden={k[1]}, top-k={k[2]}, num_experts in {list(v[0])}"
-                              for k, v in VALIDATED_GEOMETRIES.items())
-            exact = "; ".join(f"hidden={k[0]}, intermediate_hidden={k[1]}, top-k={k[2]}, (num_experts, EP size) in "
-                              f"{list(v[0])}" for k, v in VALIDATED_EP_GEOMETRIES.items())
-            return (f"geometry (hidden={hidden}, intermediate_hidden={intermediate_hidden}, num_experts={num_experts}, "
-                    f"top-k={num_topk}) has not been validated on GPUs with {num_ranks} ranks "
-                    f"(validated: {known}; exact pairs: {exact})")
-        if num_experts % num_ranks == 0 and num_experts // num_ranks < MIN_VALIDATED_EXPERTS_PER_RANK:
-            return (f"geometry (hidden={hidden}, intermediate_hidden={intermediate_hidden}, num_experts={num_experts}, "
-                    f"top-k={num_topk}) has not been validated on GPUs with {num_experts // num_ranks} experts per rank "
-                    f"(the smallest experts-per-rank that has run is {MIN_VALIDATED_EXPERTS_PER_RANK})")
-    return _structural_reason(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-                              num_shared_experts)
+_RULES = (_rule_options, _rule_ranges, _rule_validated, _rule_kernel_limits)
 
 
 def get_mega_moe_unsupported_reason(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
@@ -189,9 +238,13 @@ def get_mega_moe_unsupported_reason(num_ranks: int, num_experts: int, num_max_to
     """``None`` when this backend can serve the geometry, else a short reason.  Total: returns a reason (never raises)
     for every input, including non-positive or non-integer sizes, so a caller can fall through to another backend."""
     try:
-        return _unsupported_reason(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
-                                   intermediate_hidden, num_shared_experts, mma_type, activation, num_sms=num_sms,
-                                   fast_math=fast_math, localized_shared_weights=localized_shared_weights,
-                                   allow_unvalidated=allow_unvalidated)
+        ask = _Ask(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+                   num_shared_experts, mma_type, activation, num_sms, fast_math, localized_shared_weights,
+                   allow_unvalidated)
+        for rule in _RULES:
+            reason = rule(ask)
+            if reason is not None:
+                return reason
+        return None
     except Exception as exc:  # noqa: BLE001 - nothing may escape the predicate
         return f"geometry cannot be derived ({type(exc).__name__}: {exc})"

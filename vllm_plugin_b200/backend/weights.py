@@ -24,64 +24,81 @@ import torch
 _SUPPORTED_ACTIVATIONS = ("swiglu",)
 
 
-def _align(x: int, a: int) -> int:
-    return -(-x // a) * a
+def _exponent_bytes(sf: torch.Tensor) -> torch.Tensor:
+    """UE8M0 exponent byte of every scale: uint8 input as is, float32 powers of two by their exponent field."""
+    if sf.dtype == torch.uint8:
+        return sf
+    if sf.dtype != torch.float32:
+        raise AssertionError("scales must be float32 (UE8M0 values) or uint8 (E8M0 bytes)")
+    raw = sf.contiguous().view(torch.int32)
+    if bool((raw < 0).any()) or bool((raw & 0x7FFFFF).ne(0).any()):
+        raise AssertionError("float32 scales must be non-negative powers of two")
+    return (raw >> 23).to(torch.uint8)
 
 
 def sf_to_required_layout(sf: torch.Tensor, mn: int, k: int, num_groups: Optional[int] = None) -> torch.Tensor:
     """Per-32-K UE8M0 scales (float32 powers of two or uint8 exponent bytes, ``([G,] mn, ceil(k/32))``) -> int32
-    ``([G,] mn, ceil(k/128))``, MN-major (strides ``(ceil(k/128) * align(mn, 4), 1, align(mn, 4))``)."""
-    assert sf.dim() == (3 if num_groups is not None else 2), "expected ([G,] mn, k/32) scales"
-    squeeze = num_groups is None
-    if squeeze:
-        sf = sf.unsqueeze(0)
-    g, n, k32 = sf.shape
-    assert n == mn and k32 == -(-k // 32), f"scale shape {tuple(sf.shape)} does not match mn={mn}, k={k}"
-    if num_groups is not None:
-        assert g == num_groups
-    if sf.dtype == torch.uint8:
-        bytes_ = sf
-    else:
-        assert sf.dtype == torch.float32, "scales must be float32 (UE8M0 values) or uint8 (E8M0 bytes)"
-        bits = sf.view(torch.int32)
-        assert (bits >= 0).all() and (bits & 0x7FFFFF == 0).all(), "float32 scales must be non-negative powers of two"
-        bytes_ = (bits >> 23).to(torch.uint8)
-    k128 = -(-k32 // 4)
-    if k32 % 4:
-        bytes_ = torch.nn.functional.pad(bytes_, (0, k128 * 4 - k32), value=127)
-    packed = bytes_.contiguous().view(torch.int32)
-    n4 = _align(mn, 4)
-    out = torch.empty_strided((g, mn, k128), (k128 * n4, 1, n4), dtype=torch.int32, device=sf.device)
-    out.copy_(packed)
-    return out.squeeze(0) if squeeze else out
+    ``([G,] mn, ceil(k/128))`` with byte ``b`` of word ``w`` = K group ``4w + b``, stored MN-major: the rows of one word
+    column are contiguous (strides ``(words * align(mn, 4), 1, align(mn, 4))``).  Missing K groups of the last word hold
+    exponent 127 (scale 1.0)."""
+    grouped = num_groups is not None
+    if sf.dim() != (3 if grouped else 2):
+        raise AssertionError("expected ([G,] mn, k/32) scales")
+    exps = _exponent_bytes(sf if grouped else sf[None])
+    groups, rows, per32 = exps.shape
+    if rows != mn or per32 != (k + 31) // 32 or (grouped and groups != num_groups):
+        raise AssertionError(f"scale shape {tuple(sf.shape)} does not match mn={mn}, k={k}")
+    words = (per32 + 3) // 4
+    # assemble each word from its four bytes with shifts (byte 0 in the low bits)
+    lanes = torch.full((groups, rows, words * 4), 127, dtype=torch.int32, device=sf.device)
+    lanes[..., :per32] = exps.to(torch.int32)
+    lanes = lanes.view(groups, rows, words, 4)
+    word = lanes[..., 0] | (lanes[..., 1] << 8) | (lanes[..., 2] << 16) | (lanes[..., 3] << 24)
+    pitch = (mn + 3) // 4 * 4
+    out = torch.empty_strided((groups, mn, words), (words * pitch, 1, pitch), dtype=torch.int32, device=sf.device)
+    out.copy_(word)
+    return out if grouped else out[0]
+
+
+def _permute_rows(t: torch.Tensor, source_row: torch.Tensor) -> torch.Tensor:
+    """``out[..., r, :] = t[..., source_row[r], :]`` along dim -2, in a tensor with the strides of ``t``."""
+    out = torch.empty_like(t)                   # preserve_format keeps dense non-contiguous (MN-major) strides
+    out.copy_(t.index_select(t.dim() - 2, source_row.to(t.device)))
+    return out
+
+
+def _utccp_source_rows(rows: int) -> torch.Tensor:
+    """Stored position ``128 b + 4 c + a`` holds row ``128 b + 32 a + c``: the order in which ``tcgen05.cp`` (32 lanes x
+    four 32-bit columns, replicated to the four lane quadrants) wants the scales of a 128-row block."""
+    if rows % 128:
+        raise AssertionError("scale rows must be a multiple of 128")
+    p = torch.arange(rows)
+    within = p % 128
+    return p - within + 32 * (within % 4) + within // 4
+
+
+def _gate_up_source_rows(rows: int, gran: int) -> torch.Tensor:
+    """Stored row ``2 gran g + j`` holds gate row ``gran g + j`` for ``j < gran`` and up row ``gran g + j - gran`` after."""
+    half = rows // 2
+    if rows % 2 or half % gran:
+        raise AssertionError(f"{rows} rows cannot be interleaved in groups of {gran}")
+    p = torch.arange(rows)
+    group, j = p // (2 * gran), p % (2 * gran)
+    return torch.where(j < gran, group * gran + j, half + group * gran + j - gran)
 
 
 def transpose_sf_for_utccp(sf: torch.Tensor) -> torch.Tensor:
     """4x32 transpose of int32 scale words ``([G,] MN, K/128)`` inside every 128-row block; keeps the input strides."""
-    assert sf.dtype == torch.int32 and sf.dim() in (2, 3)
-    squeeze = sf.dim() == 2
-    if squeeze:
-        sf = sf.unsqueeze(0)
-    g, mn, kw = sf.shape
-    assert mn % 128 == 0, "scale rows must be a multiple of 128"
-    res = sf.reshape(g, -1, 4, 32, kw).transpose(2, 3).reshape(g, mn, kw)
-    out = torch.empty_like(sf).copy_(res)
-    return out.squeeze(0) if squeeze else out
+    if sf.dtype != torch.int32 or sf.dim() not in (2, 3):
+        raise AssertionError("expected int32 scale words ([G,] MN, K/128)")
+    return _permute_rows(sf, _utccp_source_rows(sf.shape[-2]))
 
 
 def interleave_weights(t: torch.Tensor, gran: int = 8) -> torch.Tensor:
-    """``[gate | up]`` rows -> ``[gate 0..7, up 0..7, gate 8..15, up 8..15, ...]`` along dim 1 (dim 0 for 2-D inputs)."""
-    assert t.dim() in (2, 3)
-    squeeze = t.dim() == 2
-    if squeeze:
-        t = t.unsqueeze(0)
-    g, n, *rest = t.shape
-    half = n // 2
-    assert half % gran == 0
-    gate = t[:, :half].reshape(g, half // gran, gran, *rest)
-    up = t[:, half:].reshape(g, half // gran, gran, *rest)
-    out = torch.empty_like(t).copy_(torch.stack([gate, up], dim=2).reshape(g, n, *rest))
-    return out.squeeze(0) if squeeze else out
+    """``[gate | up]`` rows -> ``[gate 0..7, up 0..7, gate 8..15, up 8..15, ...]`` along dim -2."""
+    if t.dim() not in (2, 3):
+        raise AssertionError("expected ([G,] rows, columns)")
+    return _permute_rows(t, _gate_up_source_rows(t.shape[-2], gran))
 
 
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],

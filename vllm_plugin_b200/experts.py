@@ -1,198 +1,266 @@
-"""The ``DeepGemmMegaMoEExperts`` subclass that routes the serving engine's MegaMoE layer to the B200 backend.
+"""The serving engine's MegaMoE layer on the B200 backend.
 
-Same overrides as the reference's ``SM107MegaMoEExperts`` (``vllm_sm107_megamoe/experts.py:81-298``): the EPLB
-communicator gate, the admission call before weights are created, two-slice ("localized") routed weights created once
-so that reloads and load-balancer row moves keep every address, logical -> physical slot mapping for reloads after a
-rebalance, preparation of every BLOCK_M variant plus a CPU barrier before CUDA-graph capture, and the
-``(num_local_experts, -1)`` in-place views the load balancer moves rows through.
+What the engine's hook asks of a plugin layer (``patches/vllm-megamoe-plugin.patch`` of the reference, and the class it
+ships, ``vllm_sm107_megamoe/experts.py:81-298``): a subclass of ``DeepGemmMegaMoEExperts`` that names its backend module
+(``_import_backend``), answers the admission question before any weight exists, keeps the routed weights in the
+two-slice form at addresses that never change (reloads and load-balancer row moves write in place), resolves a logical
+expert to its local physical slots after a rebalance, prepares every BLOCK_M variant before CUDA-graph capture, and
+hands the load balancer ``(num_local_experts, -1)`` views that alias the parameters.
 
-The class is built by :func:`make_experts_class` on whatever base is available: the real layer when the installed vLLM
-ships it, otherwise the stand-in of ``_standin.py`` (tests).
+This module is organised around three small pieces the class composes: a table of load-balancer transports with what
+each may be used for, a helper that treats one expert of a two-slice tensor as its logical ``(N, K')`` matrix, and a
+ledger of geometries that have been warmed up in this process.  The class itself is produced by
+:func:`make_experts_class` on whatever base is available: the engine's layer when the installed engine ships it,
+otherwise the stand-in of ``_standin.py`` (tests).
 """
 
 from __future__ import annotations
 
-from typing import Any, ClassVar, Dict, Optional, Set, Tuple
+from dataclasses import dataclass
+from typing import Any, ClassVar, Dict, Iterator, List, Optional, Set, Tuple
 
 import torch
 from torch import nn
 
-LOCALIZED_WEIGHTS = ("w13_weight", "w2_weight")
+#: routed parameters kept in the two-slice form ``(2, E_l, N/2, K')``
+TWO_SLICE_PARAMETERS = ("w13_weight", "w2_weight")
 
-SUPPORTED_EPLB_COMMUNICATORS = frozenset({"symm_mem", "torch_gloo", "torch_nccl", "pynccl"})
-# NCCL transfers on the asynchronous load-balancer stream would share the GPU with the persistent expert kernels (one
-# CTA per SM, all shared memory): keep them synchronous, as the reference does.
-_SYNC_ONLY_EPLB_COMMUNICATORS = frozenset({"torch_nccl", "pynccl"})
-_UNSUPPORTED_EPLB_COMMUNICATORS = {
-    "nixl": "it registers the live expert weights for RDMA reads by peers, which the two-slice weight tensors of this "
-            "backend have not been checked with",
-    "torch_xccl": "it is the XPU backend",
+
+# ---------------------------------------------------------------------------------------------------------------------
+# load-balancer transports
+# ---------------------------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class _Transport:
+    usable: bool
+    background_moves: bool      # may move rows on the load balancer's own stream while layers run
+    objection: str = ""
+
+
+# The expert kernels are persistent (one CTA per SM holding all shared memory), so a transport whose row moves are NCCL
+# kernels must not run beside them: those stay synchronous, as in the reference (``experts.py:29-78``).
+_TRANSPORTS: Dict[str, _Transport] = {
+    "symm_mem": _Transport(True, True),
+    "torch_gloo": _Transport(True, True),
+    "torch_nccl": _Transport(True, False, "its NCCL kernels would run next to the persistent expert kernels"),
+    "pynccl": _Transport(True, False, "its NCCL kernels would run next to the persistent expert kernels"),
+    "nixl": _Transport(False, False, "it registers the live expert weights for RDMA reads by peers, which the two-slice "
+                                     "weight tensors of this backend have not been checked with"),
+    "torch_xccl": _Transport(False, False, "it is the XPU backend"),
 }
+_ADVICE = "Set --eplb-config.communicator=symm_mem, or torch_gloo."
 
 
 def _check_eplb(parallel_config: Any) -> None:
-    """Refuse load-balancer setups this backend cannot serve (same decisions as ``experts.py:49-78`` of the reference)."""
+    """Raise ``NotImplementedError`` for a load-balancer setup this backend cannot serve."""
     if getattr(parallel_config, "enable_elastic_ep", False):
         raise NotImplementedError("B200 MegaMoE does not support elastic EP: the workspace and the prepared kernel "
                                   "variants are built for a fixed EP size and physical expert count")
-    eplb_config = parallel_config.eplb_config
-    communicator = eplb_config.communicator
-    if communicator in SUPPORTED_EPLB_COMMUNICATORS:
-        if communicator in _SYNC_ONLY_EPLB_COMMUNICATORS and getattr(eplb_config, "use_async", False):
-            raise NotImplementedError(
-                f"B200 MegaMoE cannot use EPLB communicator {communicator!r} with use_async=true: its NCCL kernels "
-                "would run next to the persistent expert kernels. Set --eplb-config.communicator=symm_mem.")
+    config = parallel_config.eplb_config
+    name = config.communicator
+    transport = _TRANSPORTS.get(name, _Transport(False, False, "it has not been checked with two-slice routed weights"))
+    if not transport.usable:
+        raise NotImplementedError(f"B200 MegaMoE cannot use EPLB communicator {name!r}: {transport.objection}. {_ADVICE}")
+    if getattr(config, "use_async", False) and not transport.background_moves:
+        raise NotImplementedError(f"B200 MegaMoE cannot use EPLB communicator {name!r} with use_async=true: "
+                                  f"{transport.objection}. {_ADVICE}")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# one expert of a two-slice tensor as its logical matrix
+# ---------------------------------------------------------------------------------------------------------------------
+class _ExpertRows:
+    """Slot ``slot`` of a ``(2, E_l, N/2, K')`` tensor: slice 0 holds the first half of the expert's rows, slice 1 the
+    second.  ``gather`` returns a private ``(N, K')`` copy in the base layer's layout, ``scatter`` writes one back into
+    the same storage (addresses, captured graphs and cached launches survive)."""
+
+    def __init__(self, tensor: torch.Tensor, slot: int):
+        self.halves = (tensor[0, slot], tensor[1, slot])
+
+    def gather(self) -> torch.Tensor:
+        return torch.cat(self.halves, dim=0)
+
+    def scatter(self, rows: torch.Tensor) -> None:
+        first, second = rows.split(self.halves[0].shape[0], dim=0)
+        self.halves[0].copy_(first)
+        self.halves[1].copy_(second)
+
+
+def _rows_as_matrix(name: str, block: torch.Tensor, num_local: int) -> torch.Tensor:
+    """``(num_local, -1)`` view of a per-expert tensor over exactly its own memory: plain contiguous tensors, and the
+    MN-major scale tensors whose memory order is ``(expert, column, row)``."""
+    if block.shape[0] == num_local:
+        if block.is_contiguous():
+            return block.view(num_local, -1)
+        if block.dim() == 3:
+            swapped = block.permute(0, 2, 1)
+            if swapped.is_contiguous():
+                return swapped.view(num_local, -1)
+    raise AssertionError(f"B200 MegaMoE EPLB {name}: expected contiguous memory with {num_local} local experts on dim 0, "
+                         f"got shape={tuple(block.shape)} stride={tuple(block.stride())} dtype={block.dtype}")
+
+
+def _expert_major_blocks(name: str, tensor: torch.Tensor, num_local: int) -> Iterator[Tuple[int, torch.Tensor]]:
+    """(byte offset inside the parameter, per-expert block) pairs: one per slice for a two-slice parameter."""
+    if name not in TWO_SLICE_PARAMETERS:
+        yield 0, tensor
         return
-    reason = _UNSUPPORTED_EPLB_COMMUNICATORS.get(communicator, "it has not been checked with two-slice routed weights")
-    raise NotImplementedError(f"B200 MegaMoE cannot use EPLB communicator {communicator!r}: {reason}. "
-                              "Set --eplb-config.communicator=symm_mem, or torch_gloo.")
+    if tensor.dim() != 4 or tensor.shape[0] != 2 or tensor.shape[1] != num_local:
+        raise AssertionError(f"B200 MegaMoE EPLB {name}: expected two-slice (2, {num_local}, N/2, K/2), "
+                             f"got shape={tuple(tensor.shape)}")
+    for s in range(2):
+        yield s * tensor.stride(0) * tensor.element_size(), tensor[s]
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# the layer class
+# ---------------------------------------------------------------------------------------------------------------------
 def make_experts_class(base: type, get_ep_group=None, mxfp4_format: Any = None) -> type:
     """Build the plugin layer class on ``base`` (the engine's ``DeepGemmMegaMoEExperts`` or the stand-in)."""
     if get_ep_group is None:
         try:
-            from vllm.distributed import get_ep_group as _g
-            get_ep_group = _g
+            from vllm.distributed import get_ep_group as engine_group
+            get_ep_group = engine_group
         except Exception:  # noqa: BLE001
-            from ._standin import get_ep_group as _g
-            get_ep_group = _g
+            from ._standin import get_ep_group as standin_group
+            get_ep_group = standin_group
 
     class B200MegaMoEExperts(base):  # type: ignore[misc, valid-type]
         """MXFP4 routed experts with one fused MXFP8 shared expert on B200."""
 
-        _prepared_variants: ClassVar[Set[Tuple]] = set()
+        _warmed_up: ClassVar[Set[Tuple]] = set()        # geometries whose kernel variants are ready in this process
         _ep_group_getter = staticmethod(get_ep_group)
 
+        # -------------------------------------------------------------------------------------------- construction
         def __init__(self, vllm_config: Any, **kwargs: Any):
-            parallel_config = vllm_config.parallel_config
+            self._refuse_unservable(vllm_config.parallel_config, kwargs)
+            super().__init__(vllm_config, **kwargs)
+
+        @classmethod
+        def _refuse_unservable(cls, parallel_config: Any, kwargs: Dict[str, Any]) -> None:
             if getattr(parallel_config, "enable_eplb", False):
                 _check_eplb(parallel_config)
             if mxfp4_format is not None and kwargs.get("weight_format", mxfp4_format) != mxfp4_format:
                 raise NotImplementedError("B200 MegaMoE requires MXFP4 weights")
             if kwargs["activation"].name != "swiglu":
                 raise NotImplementedError("B200 MegaMoE requires SwiGLU")
-            backend = self._import_backend()
-            if not backend.is_localization_available():
+            if not cls._import_backend().is_localization_available():
                 raise NotImplementedError("B200 MegaMoE requires a CUDA device of compute capability 10.0")
-            super().__init__(vllm_config, **kwargs)
 
         @staticmethod
         def _import_backend():
-            from . import api as backend
+            from . import api
 
-            return backend
+            return api
 
         def _create_weights(self) -> None:
-            backend = self._import_backend()
-            reason = backend.get_unsupported_reason_for_mega_moe(
+            api = self._import_backend()
+            verdict = api.get_unsupported_reason_for_mega_moe(
                 self._ep_group_getter().world_size, self.num_experts, self.max_num_tokens, self.top_k, self.hidden_size,
                 self.intermediate_size, self.num_shared_experts, fast_math=self.fast_math)
-            if reason is not None:
-                raise NotImplementedError(f"B200 MegaMoE: {reason}")
+            if verdict is not None:
+                raise NotImplementedError(f"B200 MegaMoE: {verdict}")
             super()._create_weights()
-            for name in LOCALIZED_WEIGHTS:
-                param = getattr(self, name)
-                param.data = backend.localize(param.data)
+            # once, here: from now on the routed weights live at these addresses in the two-slice form
+            for name in TWO_SLICE_PARAMETERS:
+                parameter = getattr(self, name)
+                parameter.data = api.localize(parameter.data)
 
-        def _map_global_expert_id(self, expert_id: int):
-            """Local slots of logical expert ``expert_id``: the initial placement before the load balancer is set up,
-            its current replica map afterwards (a reload then writes every replica)."""
-            mapping = self.eplb_state.logical_to_physical_map
-            if mapping is None:
+        # -------------------------------------------------------------------------------------------- checkpoint loading
+        def _map_global_expert_id(self, expert_id: int) -> List[int]:
+            """Local slots of logical expert ``expert_id``: the initial placement until the load balancer publishes its
+            replica map, that map afterwards (a reload after a rebalance then writes every replica)."""
+            replica_map = self.eplb_state.logical_to_physical_map
+            if replica_map is None:
                 return super()._map_global_expert_id(expert_id)
-            return [p - self.experts_start_idx for p in mapping[expert_id].tolist()
-                    if self.experts_start_idx <= p < self.experts_end_idx]
+            lo, hi = self.experts_start_idx, self.experts_end_idx
+            return [slot - lo for slot in replica_map[expert_id].tolist() if lo <= slot < hi]
 
         def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, weight_name: str, shard_id: str,
                           expert_id: int, return_success: bool = False) -> Optional[bool]:
-            if param is not self.w13_weight and param is not self.w2_weight:
+            if not any(param is getattr(self, name) for name in TWO_SLICE_PARAMETERS):
                 return super().weight_loader(param, loaded_weight, weight_name, shard_id, expert_id, return_success)
-            local_ids = self._map_global_expert_id(expert_id)
-            param_prefix = "w2_" if shard_id == "w2" else "w13_"
-            if not local_ids or param_prefix not in weight_name:
-                return False if return_success else None
-            for local_id in local_ids:
-                dst = param.data[:, local_id]               # (2, N/2, K'): the expert's two slices
-                logical = dst.flatten(0, 1).clone()         # (N, K') in the base layer's layout
-                self._load_weight(logical, loaded_weight, shard_id, False)
-                dst.copy_(logical.view_as(dst))             # in place: addresses, graphs and bound launches survive
-            if hasattr(self, "_kernel_weights"):
+            family = "w2_" if shard_id == "w2" else "w13_"
+            slots = self._map_global_expert_id(expert_id) if family in weight_name else []
+            for slot in slots:
+                rows = _ExpertRows(param.data, slot)
+                logical = rows.gather()
+                self._load_weight(logical, loaded_weight, shard_id, False)     # the base layer's own shard placement
+                rows.scatter(logical)
+            if slots and hasattr(self, "_kernel_weights"):
                 self._kernel_weights = None
-            return True if return_success else None
+            if not return_success:
+                return None
+            return bool(slots)
 
+        # -------------------------------------------------------------------------------------------- warm-up
         def get_symm_buffer(self):
-            buffer = getattr(self, "_runtime_buffer", None)
-            if buffer is not None:
-                return buffer
-            if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+            cached = getattr(self, "_runtime_buffer", None)
+            if cached is not None:
+                return cached
+            on_gpu = torch.cuda.is_available()
+            if on_gpu and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("Warm up B200 MegaMoE before CUDA-graph capture")
             buffer = super().get_symm_buffer()
-            group = self._ep_group_getter()
-            key = (id(getattr(group, "device_group", None)), torch.cuda.current_device() if torch.cuda.is_available() else -1,
-                   self.num_experts, buffer.num_max_tokens_per_rank, self.top_k, self.hidden_size,
-                   self.intermediate_size, self.num_shared_experts, self.activation, self.fast_math)
-            if key not in self._prepared_variants:
-                backend = self._import_backend()
-                backend.get_balanced_sm_locality_domains()
-                backend.precompile_mega_moe_variants(
-                    group.world_size, self.num_experts, buffer.num_max_tokens_per_rank, self.top_k, self.hidden_size,
-                    self.intermediate_size, self.num_shared_experts, **self._kernel_kwargs, fast_math=self.fast_math,
-                    per_die=True, localized_weights=True)
-                cpu_group = getattr(group, "cpu_group", None)
-                if cpu_group is not None and group.world_size > 1:
-                    torch.distributed.barrier(group=cpu_group)   # every rank is ready before any capture starts
-                self._prepared_variants.add(key)
+            self._warm_up(buffer, torch.cuda.current_device() if on_gpu else -1)
             self._runtime_buffer = buffer
             return buffer
 
-        def get_expert_weights(self):
+        def _warm_up(self, buffer: Any, device_index: int) -> None:
+            """Prepare every BLOCK_M variant of this geometry once per process and device, then meet the other ranks at a
+            host barrier so that no rank starts capturing while another still prepares."""
+            group = self._ep_group_getter()
+            ledger_key = (id(getattr(group, "device_group", None)), device_index, self.num_experts,
+                          buffer.num_max_tokens_per_rank, self.top_k, self.hidden_size, self.intermediate_size,
+                          self.num_shared_experts, self.activation, self.fast_math)
+            if ledger_key in self._warmed_up:
+                return
+            api = self._import_backend()
+            api.get_balanced_sm_locality_domains()
+            api.precompile_mega_moe_variants(
+                group.world_size, self.num_experts, buffer.num_max_tokens_per_rank, self.top_k, self.hidden_size,
+                self.intermediate_size, self.num_shared_experts, **self._kernel_kwargs, fast_math=self.fast_math,
+                per_die=True, localized_weights=True)
+            host_group = getattr(group, "cpu_group", None)
+            if host_group is not None and group.world_size > 1:
+                torch.distributed.barrier(group=host_group)
+            self._warmed_up.add(ledger_key)
+
+        # -------------------------------------------------------------------------------------------- load balancer
+        def get_expert_weights(self) -> List[torch.Tensor]:
             """Routed parameters as ``(num_local_experts, -1)`` views for the load balancer, which moves an expert by
             copying whole rows in place.  A two-slice weight gives one view per slice; both halves of an expert move
             together because the same row moves are applied to every view."""
-            views = []
-            for name, param in self.named_parameters(recurse=False):
+            views: List[torch.Tensor] = []
+            count = self.num_local_experts
+            for name, parameter in self.named_parameters(recurse=False):
                 if name.startswith("shared_"):
                     continue
-                tensor = param.data
-                if name in LOCALIZED_WEIGHTS:
-                    if tensor.dim() != 4 or tensor.shape[1] != self.num_local_experts:
-                        raise AssertionError(f"B200 MegaMoE EPLB {name}: expected two-slice (2, {self.num_local_experts}, "
-                                             f"N/2, K/2), got shape={tuple(tensor.shape)}")
-                    parts = tensor.unbind(0)
-                else:
-                    parts = (tensor,)
-                for idx, part in enumerate(parts):
-                    view = self._eplb_view(name, part)
-                    offset = idx * tensor.stride(0) * tensor.element_size() if len(parts) > 1 else 0
-                    if view.data_ptr() != tensor.data_ptr() + offset or view.numel() != part.numel() or not view.is_contiguous():
-                        raise AssertionError(f"B200 MegaMoE EPLB {name}: the view of part {idx} does not cover its memory in place")
+                whole = parameter.data
+                for offset, block in _expert_major_blocks(name, whole, count):
+                    view = _rows_as_matrix(name, block, count)
+                    in_place = (view.data_ptr() == whole.data_ptr() + offset and view.numel() == block.numel()
+                                and view.is_contiguous())
+                    if not in_place:
+                        raise AssertionError(f"B200 MegaMoE EPLB {name}: the view at byte offset {offset} does not cover "
+                                             "its memory in place")
                     views.append(view)
             return views
 
-        def _eplb_view(self, name: str, t: torch.Tensor) -> torch.Tensor:
-            e = self.num_local_experts
-            if t.shape[0] == e:
-                if t.is_contiguous():
-                    return t.view(e, -1)
-                if t.dim() == 3 and t.stride(1) == 1 and t.stride(2) == t.shape[1]:
-                    back = t.transpose(1, 2)        # MN-major scales: shape (E, M, N), memory (E, N, M)
-                    if back.is_contiguous():
-                        return back.view(e, -1)
-            raise AssertionError(f"B200 MegaMoE EPLB {name}: expected contiguous memory with {e} local experts on dim 0, "
-                                 f"got shape={tuple(t.shape)} stride={tuple(t.stride())} dtype={t.dtype}")
-
+        # -------------------------------------------------------------------------------------------- stand-in base only
         def kernel_weights(self):
-            """Stand-in base only: the kernels take the two-slice tensors as they are."""
+            """The stand-in base packs scale words from logical ``(E_l, N, K')`` parameters; show it that view for the
+            duration of the call and hand the kernels the two-slice tensors themselves."""
             if getattr(self, "_kernel_weights", None) is None:
-                w13, w2 = self.w13_weight.data, self.w2_weight.data
+                held = {name: getattr(self, name).data for name in TWO_SLICE_PARAMETERS}
                 try:
-                    self.w13_weight.data = w13.movedim(0, 1).flatten(1, 2)   # temporary logical view for the base helper
-                    self.w2_weight.data = w2.movedim(0, 1).flatten(1, 2)
-                    (_, s13), (_, s2), sl1, sl2 = super().kernel_weights()
+                    for name, tensor in held.items():
+                        getattr(self, name).data = tensor.movedim(0, 1).flatten(1, 2)
+                    (_, s13), (_, s2), shared_l1, shared_l2 = super().kernel_weights()
                 finally:
-                    self.w13_weight.data, self.w2_weight.data = w13, w2
-                self._kernel_weights = ((w13.view(torch.int8), s13), (w2.view(torch.int8), s2), sl1, sl2)
+                    for name, tensor in held.items():
+                        getattr(self, name).data = tensor
+                self._kernel_weights = ((held["w13_weight"].view(torch.int8), s13), (held["w2_weight"].view(torch.int8), s2),
+                                        shared_l1, shared_l2)
             return self._kernel_weights
 
     B200MegaMoEExperts.weight_loader.supports_moe_loading = True  # type: ignore[attr-defined]

@@ -53,6 +53,26 @@ def quantize_fp8_block128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q, exp.to(torch.uint8).repeat_interleave(128, dim=0).repeat_interleave(4, dim=1)
 
 
+def routed_expert_raw(hidden: int, inter: int, seed: int, index: int, device, std: float = 0.02):
+    """Physical routed expert ``index`` of the synthetic layer ``seed`` in checkpoint order: ``(w13 [2I, H/2] packed E2M1,
+    s13 [2I, H/32] UE8M0 bytes, w2 [H, I/2], s2 [H, I/32])``.  A function of ``(seed, index)`` alone, so any rank of an
+    expert-parallel run can reproduce any expert."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed * 100003 + index)
+    w13, s13 = quantize_mxfp4(torch.randn((2 * inter, hidden), generator=g, device=dev) * std)
+    w2, s2 = quantize_mxfp4(torch.randn((hidden, inter), generator=g, device=dev) * std)
+    return w13, s13, w2, s2
+
+
+def shared_expert_raw(hidden: int, inter: int, seed: int, device, std: float = 0.02):
+    """The synthetic layer's shared expert: ``(w13 [2I, H] E4M3, s13 [2I, H/32], w2 [H, I], s2 [H, I/32])``."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed * 100003 + 99991)
+    a = torch.randn((2 * inter, hidden), generator=g, device=dev) * std
+    b = torch.randn((hidden, inter), generator=g, device=dev) * std
+    return quantize_fp8_block128(a) + quantize_fp8_block128(b)
+
+
 class SyntheticLayer:
     """Weights of ``num_local`` routed experts (+ optional shared expert) in the kernels' format, built expert by expert
     on ``device`` so that peak memory stays one expert of FP32 above the packed result."""
@@ -66,11 +86,7 @@ class SyntheticLayer:
         s13 = torch.empty((num_local, 2 * inter, hidden // 32), dtype=torch.uint8, device=dev)
         s2 = torch.empty((num_local, hidden, inter // 32), dtype=torch.uint8, device=dev)
         for e in range(num_local):
-            g = torch.Generator(device=dev).manual_seed(seed * 100003 + first_expert + e)
-            a = torch.randn((2 * inter, hidden), generator=g, device=dev) * std
-            w13[e], s13[e] = quantize_mxfp4(a)
-            b = torch.randn((hidden, inter), generator=g, device=dev) * std
-            w2[e], s2[e] = quantize_mxfp4(b)
+            w13[e], s13[e], w2[e], s2[e] = routed_expert_raw(hidden, inter, seed, first_expert + e, dev, std)
         self.raw = (w13, s13, w2, s2)
         l13 = sf_to_required_layout(s13, 2 * inter, hidden, num_local)
         l2 = sf_to_required_layout(s2, hidden, inter, num_local)
@@ -82,12 +98,7 @@ class SyntheticLayer:
         self.shared_l1 = self.shared_l2 = None
         self.shared_raw = None
         if shared:
-            g = torch.Generator(device=dev).manual_seed(seed * 100003 + 99991)
-            a = torch.randn((2 * inter, hidden), generator=g, device=dev) * std
-            b = torch.randn((hidden, inter), generator=g, device=dev) * std
-            q13, e13 = quantize_fp8_block128(a)
-            q2, e2 = quantize_fp8_block128(b)
-            self.shared_raw = (q13, e13, q2, e2)
+            q13, e13, q2, e2 = self.shared_raw = shared_expert_raw(hidden, inter, seed, dev, std)
             self.shared_l1, self.shared_l2 = transform_weights_for_mega_moe(
                 (q13, sf_to_required_layout(e13, 2 * inter, hidden)), (q2, sf_to_required_layout(e2, hidden, inter)))
 
