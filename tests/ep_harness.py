@@ -26,7 +26,7 @@ def free_port() -> int:
 
 def _entry(rank, world, backend, port, fn, args, errors):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     try:
         from datetime import timedelta
         limit = timedelta(seconds=90)          # a rank that failed must not keep the others waiting for long
@@ -60,8 +60,12 @@ def run_ranks(world: int, backend: str, fn, *args, timeout: float = 600.0) -> No
         if msgs or any(p.exitcode not in (None, 0) for p in procs):
             break                     # one rank failed: do not wait for the others' collective timeouts
         time.sleep(0.2)
-    if msgs:
-        time.sleep(1.0)
+    # After a failure the other ranks leave by themselves: their device-side waits are bounded (seconds) and their next
+    # collective ends with the process group's timeout.  Give them that long; a rank is killed only as the last resort
+    # (it holds a symmetric workspace, so a clean exit is preferred).
+    grace = time.time() + (110.0 if msgs or any(p.exitcode not in (None, 0) for p in procs) else 0.0)
+    while time.time() < grace and any(p.is_alive() for p in procs):
+        time.sleep(0.5)
     hung = [p for p in procs if p.is_alive()]
     for p in hung:
         p.kill()                      # the exact processes started above

@@ -49,6 +49,45 @@ def test_peer_wait_times_out_and_reports_status():
     rid, w = O.make_routing(5, 8, 2, 2)
     y, _ = H.run_layer(layer, hid, rid, w)
     assert O.parity_metrics(y.cpu(), H.oracle_layer(layer, hid, rid, w))["rel_l2"] <= 1e-3
+    # reading the status cleared it: the buffer that timed out reports healthy again
+    assert lib.mmoe_read_status(geo, mine.base_ptr, words, stream) == _native.MMOE_OK and words[0] == 0
+
+
+def test_eager_calls_notice_a_bad_status_without_blocking():
+    """The production path never calls ``read_status``: eager calls copy the status words to pinned memory behind the
+    launch (here after every call) and a later call raises.  The condition used is an expert id >= num_experts, which the
+    dispatch counts and treats as masked; after the report the buffer is healthy again."""
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend.workspace import SingleRankGroup
+    import helpers as H
+    from helpers import O
+    layer = H.make_layer(512, 256, 8, 2, True, seed=3)
+    l1, l2, sl1, sl2 = H.kernel_weights(layer, "cuda")
+    buf = api.get_symm_buffer_for_mega_moe(SingleRankGroup(), 8, 1920, 2, 512, 256, 1)
+    hid = O.make_hidden(6, 512, 1).cuda()
+    ids, w = O.make_routing(6, 8, 2, 2)
+    bad = ids.clone()
+    bad[0, 0] = 99
+    y = torch.empty((6, 512), dtype=torch.bfloat16, device="cuda")
+    api.set_kernel_options(status_poll_interval=1)
+    try:
+        def call(which):
+            api.stage_inputs_for_mega_moe(buf, hid, which.cuda(), w.cuda())
+            api.fp8_fp4_mega_moe(y, l1, l2, buf, sl1, sl2, activation_clamp=10.0)
+        call(bad)
+        torch.cuda.synchronize()
+        with pytest.raises(AssertionError, match="expert ids"):
+            for _ in range(3):                 # the copy was queued behind the first call; one of the next calls sees it
+                call(ids)
+                torch.cuda.synchronize()
+        for _ in range(3):                     # re-armed: healthy calls stay quiet
+            call(ids)
+            torch.cuda.synchronize()
+        api.read_status(buf)
+    finally:
+        api.set_kernel_options(status_poll_interval=32)
+    ref = H.oracle_layer(layer, hid.cpu(), ids, w)
+    assert O.parity_metrics(y.cpu(), ref)["rel_l2"] <= 1e-3
 
 
 def test_host_side_argument_errors_map_to_the_reference_exception_classes():

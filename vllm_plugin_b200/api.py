@@ -97,6 +97,14 @@ def precompile_mega_moe_variants(num_ranks: int, num_experts: int, num_max_token
                  localized_weights=localized_weights, localized_shared_weights=localized_shared_weights)
 
 
+def read_status(sym_buffer) -> None:
+    """Synchronise and raise if a device-side wait expired (``RuntimeError``) or an expert id was out of range
+    (``AssertionError``) in any call on ``sym_buffer`` since the last read; clears the condition."""
+    from .backend.frontend import read_status as _impl
+
+    return _impl(sym_buffer)
+
+
 def set_kernel_options(**kwargs):
     from .backend.frontend import set_kernel_options as _impl
 
@@ -146,5 +154,5 @@ __all__ = [
     "get_symm_buffer_for_mega_moe", "transform_weights_for_mega_moe", "fp8_fp4_mega_moe", "get_block_m_for_mega_moe",
     "get_token_alignment_for_mega_moe", "get_unsupported_reason_for_mega_moe", "stage_inputs_for_mega_moe",
     "precompile_mega_moe_variants", "set_kernel_options", "get_kernel_options", "is_localization_available",
-    "get_balanced_sm_locality_domains", "localize", "localize_mega_moe_weights", "SymmBuffer",
+    "get_balanced_sm_locality_domains", "localize", "localize_mega_moe_weights", "read_status", "SymmBuffer",
 ]

@@ -4,8 +4,13 @@ sequence of one forward call.  Mirrors ``backend/frontend.py`` of the reference 
 ``precompile_mega_moe_variants`` :851-897) on top of the C ABI of ``libmmoe_b200.so``.
 
 At EP = 1 one call is: route ordering -> pool placement -> grouped GEMM1 (+SwiGLU/requant) -> grouped GEMM2 -> combine.
-At EP > 1 three NCCL exchanges sit between those steps (per-expert counts, rows out, rows back), issued through
-``torch.distributed`` on the caller's group; the expert shards need no other collective.
+At EP > 1 the default transport is the device-side exchange over NVLink peer memory (``mmoe_forward_ep``: counts and rows
+pushed into the peers' symmetric workspaces, GEMM2 writing its rows straight back to the rank they came from); the
+host-driven alternative issues the same three exchanges as ``torch.distributed`` all-to-allv calls on the caller's group.
+
+Like the reference (``frontend.py:650-754``) a call with the tensors of the previous call skips the argument checks: the
+record of the last validated call is kept on the buffer, and a call whose weight tensors are the same objects at the same
+addresses goes straight to the launch.
 """
 
 from __future__ import annotations
@@ -34,6 +39,8 @@ class KernelOptions:
     fuse_return: bool = True    # "peer" transport: GEMM2's epilogue stores its rows straight into the source rank's
                                 # buffer over NVLink, and the dispatch overlaps the shared expert's GEMMs on a second
                                 # stream; False = one stream, separate copy kernel after GEMM2 (same result)
+    status_poll_interval: int = 32   # eager calls between two non-blocking reads of the device status words (a bounded
+                                     # wait that expired, an expert id out of range); 0 = never, 1 = every call
     orientation: int = 0        # grouped-GEMM kernel family: 0 = chosen per call from the expected rows per expert,
                                 # 1 = weights-as-A (small token counts) always, 2 = tokens-as-A wherever the geometry
                                 # allows, 3 = tokens-as-A on CTA pairs; every rank of a group must use the same value
@@ -208,65 +215,157 @@ def exchange_rows(group, dst: torch.Tensor, src: torch.Tensor, dst_splits, src_s
     dist.all_to_all_single(d, s, list(dst_splits), list(src_splits), group=group)
 
 
+class _CallRecord:
+    """What the last validated call on a buffer established: the tensor objects it checked (kept alive, so that their
+    identities cannot be reused), the structures built from them, and the status poll state."""
+
+    __slots__ = ("tensors", "addresses", "weights", "stats", "options_key", "options", "peers", "variants_ready")
+
+    def matches(self, tensors) -> bool:
+        kept = self.tensors
+        for a, b, addr in zip(tensors, kept, self.addresses):
+            if a is not b or (a is not None and a.data_ptr() != addr):
+                return False
+        return True
+
+
+class _StatusPoll:
+    """Non-blocking watch on the device status words of one buffer: every ``interval`` eager calls the words are copied
+    to pinned host memory behind the call; a later call that finds the copy complete inspects it."""
+
+    def __init__(self, sym_buffer):
+        self.host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.calls = 0
+
+    def before_call(self, sym_buffer) -> None:
+        if self.pending and self.event.query():
+            self.pending = False
+            words = self.host.tolist()
+            if words[0] != 0 or words[4] != 0:
+                sym_buffer.status.zero_()                      # re-arm: the next healthy call reports healthy
+                if words[0] != 0:
+                    raise RuntimeError(f"a device-side wait of an earlier MegaMoE call expired (kernel {words[1]}, role "
+                                       f"{words[2]}, block {words[3]}): its output is not valid")
+                raise AssertionError(f"{words[4]} expert ids of an earlier MegaMoE call were >= num_experts")
+
+    def after_call(self, sym_buffer, interval: int) -> None:
+        self.calls += 1
+        if interval > 0 and not self.pending and self.calls % interval == 0:
+            self.host.copy_(sym_buffer.status, non_blocking=True)
+            self.event.record()
+            self.pending = True
+
+
+def _validate(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights, stats, recipe, activation,
+              activation_clamp, fast_math, activation_alpha, activation_beta, tensors) -> _CallRecord:
+    require_sm100()
+    s13, s2 = check_mega_moe_arguments(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights,
+                                       stats, recipe, activation, activation_clamp, fast_math, activation_alpha,
+                                       activation_beta)
+    rec = _CallRecord()
+    rec.tensors = tensors
+    rec.addresses = tuple(t.data_ptr() if t is not None else 0 for t in tensors)
+    rec.weights = _weights_struct(l1_weights, l2_weights, shared_l1_weights, shared_l2_weights, s13, s2)
+    rec.options_key = None
+    rec.options = None
+    rec.peers = None
+    if sym_buffer.peer_ptrs is not None:
+        rec.peers = (ctypes.c_void_p * sym_buffer.num_ranks)(*sym_buffer.peer_ptrs)
+    rec.variants_ready = False
+    return rec
+
+
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared_l1_weights=None, shared_l2_weights=None,
                      cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
                      activation_clamp: Optional[float] = None, fast_math: bool = True, activation_alpha: float = 1.0,
                      activation_beta: float = 0.0) -> None:
     """One MegaMoE layer call for this rank: reads the staged inputs of ``sym_buffer`` (first ``y.size(0)`` tokens),
-    writes ``y``.  Launches on the current stream and never synchronises at EP = 1."""
-    require_sm100()
-    s13, s2 = check_mega_moe_arguments(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights,
-                                       cumulative_local_expert_recv_stats, recipe, activation, activation_clamp,
-                                       fast_math, activation_alpha, activation_beta)
-    lib = _native.load()
-    geo = sym_buffer.geo
+    writes ``y``.  Launches on the current stream and never synchronises (the host-driven NCCL transport aside)."""
+    stats = cumulative_local_expert_recv_stats
+    tensors = (l1_weights[0], l1_weights[1], l2_weights[0], l2_weights[1],
+               shared_l1_weights[0] if shared_l1_weights is not None else None,
+               shared_l1_weights[1] if shared_l1_weights is not None else None,
+               shared_l2_weights[0] if shared_l2_weights is not None else None,
+               shared_l2_weights[1] if shared_l2_weights is not None else None, stats)
+    rec = getattr(sym_buffer, "_call_record", None)
     m = y.size(0)
-    bm = get_block_m_for_mega_moe(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank, m,
-                                  sym_buffer.num_topk, sym_buffer.mma_type)
-    opts = _native.MmoeOptions(float(activation_clamp) if activation_clamp is not None else math.inf,
-                               1 if fast_math else 0, _kernel_options.engine, _kernel_options.timeout_ms)
-    if opts.engine == _native.ENGINE_TENSOR_CORE:
+    if (rec is None or not rec.matches(tensors) or tuple(recipe) != (1, 1, 32) or activation != "swiglu"
+            or activation_alpha != 1.0 or activation_beta != 0.0):
+        rec = _validate(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights, stats, recipe,
+                        activation, activation_clamp, fast_math, activation_alpha, activation_beta, tensors)
+        sym_buffer._call_record = rec
+    else:
+        # the record vouches for everything but the output tensor and the clamp
+        assert y.dim() == 2 and y.size(1) == sym_buffer.hidden and y.dtype == torch.bfloat16 and y.is_contiguous(), \
+            "y must be contiguous BF16 (M, H)"
+        assert y.is_cuda and y.data_ptr() % 16 == 0, "y must be a 16-byte aligned CUDA tensor"
+        assert m <= sym_buffer.num_max_tokens_per_rank, "num_tokens must be <= num_max_tokens_per_rank"
+        assert activation_clamp is None or activation_clamp > 0, "activation_clamp must be positive"
+    ko = _kernel_options
+    key = (activation_clamp, bool(fast_math), ko.engine, ko.timeout_ms)
+    if rec.options_key != key:
+        rec.options = _native.MmoeOptions(float(activation_clamp) if activation_clamp is not None else math.inf,
+                                          1 if fast_math else 0, ko.engine, ko.timeout_ms)
+        rec.options_key = key
+    capturing = torch.cuda.is_current_stream_capturing()
+    if not rec.variants_ready and ko.engine == _native.ENGINE_TENSOR_CORE and not capturing:
         precompile_mega_moe_variants(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank,
                                      sym_buffer.num_topk, sym_buffer.hidden, sym_buffer.intermediate_hidden,
-                                     sym_buffer.num_shared_experts) if not torch.cuda.is_current_stream_capturing() else None
-    w = _weights_struct(l1_weights, l2_weights, shared_l1_weights, shared_l2_weights, s13, s2)
-    stats_ptr = cumulative_local_expert_recv_stats.data_ptr() if cumulative_local_expert_recv_stats is not None else None
+                                     sym_buffer.num_shared_experts)
+        rec.variants_ready = True
+    poll = None
+    if ko.status_poll_interval > 0 and not capturing:
+        poll = getattr(sym_buffer, "_status_poll", None)
+        if poll is None:
+            poll = sym_buffer._status_poll = _StatusPoll(sym_buffer)
+        poll.before_call(sym_buffer)
+    lib = _native.load()
+    bm = get_block_m_for_mega_moe(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank, m,
+                                  sym_buffer.num_topk, sym_buffer.mma_type)
+    w, opts = ctypes.byref(rec.weights), ctypes.byref(rec.options)
+    stats_ptr = stats.data_ptr() if stats is not None else None
     stream = torch.cuda.current_stream(y.device).cuda_stream
     ws = sym_buffer.base_ptr
-    g = ctypes.byref(geo)
+    g = ctypes.byref(sym_buffer.geo)
     if sym_buffer.num_ranks == 1:
-        _native.check(lib.mmoe_forward(g, ws, ctypes.byref(w), ctypes.byref(opts), y.data_ptr(), m, bm, stats_ptr, stream))
-        return
-    group = sym_buffer.group
-    if sym_buffer.peer_ptrs is not None and _kernel_options.ep_transport == "peer":
+        _native.check(lib.mmoe_forward(g, ws, w, opts, y.data_ptr(), m, bm, stats_ptr, stream))
+    elif rec.peers is not None and ko.ep_transport == "peer":
         # device-side exchange: no host round trip, capturable in a CUDA graph
-        peers = (ctypes.c_void_p * sym_buffer.num_ranks)(*sym_buffer.peer_ptrs)
-        if _kernel_options.fuse_return:
-            _native.check(lib.mmoe_forward_ep(g, ws, peers, ctypes.byref(w), ctypes.byref(opts), y.data_ptr(), m, bm,
-                                              stats_ptr, stream))
-            return
+        peers = rec.peers
+        if ko.fuse_return:
+            _native.check(lib.mmoe_forward_ep(g, ws, peers, w, opts, y.data_ptr(), m, bm, stats_ptr, stream))
+        else:
+            _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
+            _native.check(lib.mmoe_ep_dispatch(g, ws, peers, m, opts, stream))
+            _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
+            _native.check(lib.mmoe_experts(g, ws, w, opts, m, bm, stream))
+            _native.check(lib.mmoe_ep_return(g, ws, peers, opts, stream))
+            _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
+    else:
+        group = sym_buffer.group
         _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
-        _native.check(lib.mmoe_ep_dispatch(g, ws, peers, m, ctypes.byref(opts), stream))
+        _native.check(lib.mmoe_dispatch_pack(g, ws, m, stream))
+        send_splits, recv_splits = exchange_counts(group, sym_buffer.send_count, sym_buffer.recv_count)
+        exchange_rows(group, sym_buffer.recv_x, sym_buffer.send_x, recv_splits, send_splits)
+        exchange_rows(group, sym_buffer.recv_sf, sym_buffer.send_sf, recv_splits, send_splits)
+        exchange_rows(group, sym_buffer.recv_w, sym_buffer.send_w, recv_splits, send_splits)
         _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
-        _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
-        _native.check(lib.mmoe_ep_return(g, ws, peers, ctypes.byref(opts), stream))
+        _native.check(lib.mmoe_experts(g, ws, w, opts, m, bm, stream))
+        exchange_rows(group, sym_buffer.ret_recv, sym_buffer.ret, send_splits, recv_splits)
         _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
-        return
-    _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
-    _native.check(lib.mmoe_dispatch_pack(g, ws, m, stream))
-    send_splits, recv_splits = exchange_counts(group, sym_buffer.send_count, sym_buffer.recv_count)
-    exchange_rows(group, sym_buffer.recv_x, sym_buffer.send_x, recv_splits, send_splits)
-    exchange_rows(group, sym_buffer.recv_sf, sym_buffer.send_sf, recv_splits, send_splits)
-    exchange_rows(group, sym_buffer.recv_w, sym_buffer.send_w, recv_splits, send_splits)
-    _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
-    _native.check(lib.mmoe_experts(g, ws, ctypes.byref(w), ctypes.byref(opts), m, bm, stream))
-    exchange_rows(group, sym_buffer.ret_recv, sym_buffer.ret, send_splits, recv_splits)
-    _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
+    if poll is not None:
+        poll.after_call(sym_buffer, ko.status_poll_interval)
 
 
 def read_status(sym_buffer) -> None:
-    """Synchronise and raise if a device-side wait expired or the dispatch saw an out-of-range expert id."""
+    """Synchronise, read the device status words of the buffer and clear them; raises ``RuntimeError`` if a bounded
+    device-side wait expired in any call since the last read (the output of that call is not valid) and
+    ``AssertionError`` if the dispatch saw expert ids >= ``num_experts`` (they were treated as masked).  After the read
+    the buffer reports healthy again.  Eager calls also watch the words without blocking, see
+    ``KernelOptions.status_poll_interval``."""
     words = (ctypes.c_int32 * 8)()
     stream = torch.cuda.current_stream(sym_buffer.device).cuda_stream
     _native.check(_native.load().mmoe_read_status(ctypes.byref(sym_buffer.geo), sym_buffer.base_ptr, words, stream))

@@ -4,9 +4,11 @@ Mirrors ``backend/workspace.py`` of the reference: the attributes a serving engi
 (``x``, ``x_sf``, ``topk_idx``, ``topk_weights``, ``shared_l1_acts_sf`` and the *aligned* ``num_max_tokens_per_rank``,
 ``workspace.py:72-76``), the token capacity is rounded up to 1920 (``workspace.py:92-95``), the buffer is zeroed and the
 group synchronised once at creation (``workspace.py:129-131``).  The regions behind the engine-facing views belong to
-the B200 kernels and are laid out by the C library (``mmoe_layout``); at EP > 1 the exchange between ranks is an NCCL
-all-to-allv between the ``send_*`` / ``recv_*`` / ``ret`` regions instead of in-kernel NVLink stores, so the buffer is
-ordinary device memory on every rank.
+the B200 kernels and are laid out by the C library (``mmoe_layout``).  At EP > 1 the buffer is a symmetric allocation
+(``torch.distributed._symmetric_memory``, as in the reference, ``workspace.py:125-128``): every rank holds every peer's
+base pointer and the exchange kernels store counts and rows straight into the peers' ``recv_*`` / ``ret_recv`` regions
+over NVLink (plain peer stores: no multicast object is bound to the allocation).  When symmetric memory cannot be set up
+on ANY rank, every rank falls back together to ordinary device memory and the host-driven NCCL all-to-allv.
 """
 
 from __future__ import annotations
@@ -48,19 +50,8 @@ class SymmBuffer:
         self.peer_ptrs = None          # EP > 1: every rank's buffer mapped into this process (symmetric allocation)
         self.handle = None
         if group.size() > 1 and device.type == "cuda":
-            try:
-                import torch.distributed._symmetric_memory as symm_mem
-
-                self.buffer = symm_mem.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
-                self.handle = symm_mem.rendezvous(self.buffer, group)
-                self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
-                assert self.peer_ptrs[group.rank()] == self.buffer.data_ptr()
-            except Exception as exc:  # noqa: BLE001 - no symmetric memory: the host-driven NCCL exchange still works
-                warnings.warn(f"symmetric memory is unavailable ({type(exc).__name__}: {exc}); using the NCCL exchange")
-                self.peer_ptrs = None
-                self.handle = None
-                self.buffer = torch.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
-        else:
+            self._allocate_symmetric(group, device)
+        if getattr(self, "buffer", None) is None:
             self.buffer = torch.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
         assert self.buffer.data_ptr() % 1024 == 0
         self.buffer.zero_()
@@ -71,6 +62,38 @@ class SymmBuffer:
                 work.wait()
         torch.cuda.synchronize(device)
         self._build_views()
+
+    def _allocate_symmetric(self, group, device) -> None:
+        """Symmetric allocation + rendezvous; the outcome is agreed on by the whole group, so that no rank runs the peer
+        transport while another runs the NCCL one."""
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer stores only
+        problem = None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.buffer = symm_mem.empty(self.layout.total_bytes, dtype=torch.int8, device=device)
+            self.handle = symm_mem.rendezvous(self.buffer, group)
+            self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            assert self.peer_ptrs[group.rank()] == self.buffer.data_ptr()
+        except Exception as exc:  # noqa: BLE001 - no symmetric memory: the host-driven NCCL exchange still works
+            problem = f"{type(exc).__name__}: {exc}"
+        everyone_ok = problem is None
+        try:
+            import torch.distributed as dist
+
+            if isinstance(group, dist.ProcessGroup):
+                flag = torch.tensor([1 if problem is None else 0], dtype=torch.int32, device=device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+                everyone_ok = bool(flag.item())
+        except Exception:  # noqa: BLE001 - a group that cannot reduce keeps this rank's own outcome
+            pass
+        if not everyone_ok:
+            warnings.warn(f"symmetric memory is unavailable ({problem or 'on another rank'}); using the NCCL exchange")
+            self.peer_ptrs = None
+            self.handle = None
+            self.buffer = None
 
     # ---------------------------------------------------------------------------------------------------- views
     def _view(self, offset: int, shape, dtype, strides=None) -> torch.Tensor:

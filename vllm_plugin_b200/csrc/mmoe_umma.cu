@@ -25,6 +25,9 @@
 // of the rank the token came from (plain peer stores over NVLink, no TMA from or to peer memory), and `tile_select`
 // restricts a launch to the routed tiles or to the shared expert's tiles planned ahead, so that the shared expert can
 // run while the dispatch is still in flight on another stream.
+#include <string.h>
+
+#include <mutex>
 #include <type_traits>
 
 #include "mmoe_tc.cuh"
@@ -532,9 +535,51 @@ cudaError_t launch_layer(const UmmaParams& p, int box, cudaStream_t s) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Launch parameters that depend only on (workspace, weights, geometry, kernel family) -- above all the encoded tensor
+// maps -- are built once and kept: a serving engine calls the layer with the same buffers thousands of times, and
+// encoding two dozen tensor maps per call costs more host time than the launches themselves.  What changes per call
+// (tile selection, options, peers) is patched into a copy.  The reference keeps the same kind of record per validated
+// call (backend/frontend.py:650-754).
+// ---------------------------------------------------------------------------------------------------------------
+struct PlanKey {
+  const void* ws;
+  const void* w[8];
+  int64_t s13, s2;
+  MmoeGeometry geo;
+  int family;
+  int has_shared;
+  int device;
+  bool operator==(const PlanKey& o) const { return memcmp(this, &o, sizeof(PlanKey)) == 0; }
+};
+struct PlanEntry {
+  PlanKey key;
+  uint64_t stamp = 0;          // 0 = empty
+  UmmaParams sa[2];
+  TmParams tm[2];
+};
+constexpr int kPlanCacheSize = 16;
+PlanEntry g_plans[kPlanCacheSize];
+uint64_t g_plan_clock = 0;
+std::mutex g_plan_mutex;
+
+PlanKey make_key(const Ctx& c, const MmoeWeights& w, bool has_shared) {
+  PlanKey k;
+  memset(&k, 0, sizeof k);           // padding bytes take part in the comparison
+  k.ws = c.ws;
+  const void* ptrs[8] = {w.w13, w.w13_sf, w.w2, w.w2_sf, w.shared_w13, w.shared_w13_sf, w.shared_w2, w.shared_w2_sf};
+  for (int i = 0; i < 8; ++i) k.w[i] = ptrs[i];
+  k.s13 = w.w13_slice_stride;
+  k.s2 = w.w2_slice_stride;
+  k.geo = c.geo;
+  k.family = c.family;
+  k.has_shared = has_shared ? 1 : 0;
+  k.device = current_device();
+  return k;
+}
+
 // tokens-as-A form: both layers through mmoe_umma_tm.cu
-cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, bool has_shared,
-                              int64_t timeout_ns, cudaStream_t s) {
+bool build_tm(const Ctx& c, const MmoeWeights& w, bool has_shared, TmParams* out) {
   const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
   TmParams p1{};
   int bad = 0;
@@ -552,7 +597,7 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
     if (has_shared) bad |= make_token_map(&p1.map_tok_shared[b], c.ws + c.lay.x, h, x_rows, kBoxes[b]);
     else p1.map_tok_shared[b] = p1.map_tok_routed[b];
   }
-  if (bad) return cudaErrorInvalidValue;
+  if (bad) return false;
   p1.plan = c.ws + c.lay.plan;
   p1.wsf_routed = static_cast<const int32_t*>(w.w13_sf);
   p1.wsf_shared = static_cast<const int32_t*>(w.shared_w13_sf);
@@ -568,7 +613,6 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
   p1.act_sf_rows_shared = c.lay.shared_sf_rows;
   p1.pool_w = c.at<float>(c.lay.pool_w);
   p1.status = c.at<int32_t>(c.lay.status);
-  p1.timeout_ns = timeout_ns;
   p1.e_local = el;
   p1.num_ranks = c.geo.num_ranks;
   p1.k_dim = h;
@@ -576,10 +620,7 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
   p1.routed_sliced = w.w13_slice_stride > 0 ? 1 : 0;
   p1.hidden = h;
   p1.inter = inter;
-  p1.clamp = o.activation_clamp;
-  p1.fast_math = o.fast_math;
   p1.has_shared_weights = has_shared ? 1 : 0;
-  p1.tile_select = c.tile_select;
   p1.early_shared_first = c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens);
   p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
 
@@ -592,7 +633,7 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
     if (has_shared) bad |= make_token_map(&p2.map_tok_shared[b], c.ws + c.lay.shared_act_x, inter, x_rows, kBoxes[b]);
     else p2.map_tok_shared[b] = p2.map_tok_routed[b];
   }
-  if (bad) return cudaErrorInvalidValue;
+  if (bad) return false;
   p2.wsf_routed = static_cast<const int32_t*>(w.w2_sf);
   p2.wsf_shared = static_cast<const int32_t*>(w.shared_w2_sf);
   p2.tsf_routed = c.at<int32_t>(c.lay.act_sf);
@@ -600,24 +641,102 @@ cudaError_t launch_experts_tm(const Ctx& c, const MmoeWeights& w, const MmoeOpti
   p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
   p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
   p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
-  bool fused = false;
-  if (c.peer_ws != nullptr && c.geo.num_ranks > 1 && c.tile_select != 2) {
-    fused = true;
-    p2.ep_me = c.geo.rank;
-    p2.ep_totals = reinterpret_cast<const int32_t*>(c.ws + c.lay.ep_sync + ep_totals_offset());
-    for (int r = 0; r < c.geo.num_ranks; ++r)
-      p2.ep_ret_recv[r] = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(const_cast<void*>(c.peer_ws[r])) + c.lay.ret_recv);
-  }
   p2.k_dim = inter;
   p2.rows_per_expert = h;
   p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
+  out[0] = p1;
+  out[1] = p2;
+  return true;
+}
 
-  const int mask = o.layer_mask == 0 ? 3 : o.layer_mask;
-  cudaError_t e = cudaSuccess;
-  if (mask & 1) e = tm_launch(1, false, ctas, p1, s);
-  if (e != cudaSuccess) return e;
-  if (mask & 2) e = tm_launch(2, fused, ctas, p2, s);
-  return e;
+bool build_sa(const Ctx& c, const MmoeWeights& w, bool has_shared, UmmaParams* out) {
+  const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
+  UmmaParams p1{};
+  int bad = 0;
+  bad |= make_w13_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
+  if (has_shared) bad |= make_w13_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
+  else p1.map_w_shared = p1.map_w_routed;
+  // token maps: one per box size a tile can pick (a launch never picks one above its kernel's own box)
+  const uint32_t kBoxes[5] = {16, 32, 64, 80, 128};
+  for (int b = 0; b < 5; ++b) {
+    bad |= make_token_map(&p1.map_tok_routed_box[b], c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b]);
+    if (has_shared) bad |= make_token_map(&p1.map_tok_shared_box[b], c.ws + c.lay.x, h, c.geo.num_max_tokens, kBoxes[b]);
+    else p1.map_tok_shared_box[b] = p1.map_tok_routed_box[b];
+  }
+  if (bad) return false;
+  p1.plan = c.ws + c.lay.plan;
+  p1.wsf_routed = static_cast<const int32_t*>(w.w13_sf);
+  p1.wsf_shared = static_cast<const int32_t*>(w.shared_w13_sf);
+  p1.tsf_routed = c.at<int32_t>(c.lay.pool_sf);
+  p1.tsf_shared = c.at<int32_t>(c.lay.shared_x_sf);
+  p1.tsf_rows_routed = c.lay.pool_sf_rows;
+  p1.tsf_rows_shared = c.lay.shared_sf_rows;
+  p1.act_routed = c.at<uint8_t>(c.lay.act_x);
+  p1.act_shared = c.at<uint8_t>(c.lay.shared_act_x);
+  p1.act_sf_routed = c.at<uint8_t>(c.lay.act_sf);
+  p1.act_sf_shared = c.at<uint8_t>(c.lay.shared_act_sf);
+  p1.act_sf_rows_routed = c.lay.pool_sf_rows;
+  p1.act_sf_rows_shared = c.lay.shared_sf_rows;
+  p1.pool_w = c.at<float>(c.lay.pool_w);
+  p1.status = c.at<int32_t>(c.lay.status);
+  p1.e_local = el;
+  p1.num_ranks = c.geo.num_ranks;
+  p1.k_dim = h;
+  p1.rows_per_expert = 2 * inter;
+  p1.routed_sliced = w.w13_slice_stride > 0 ? 1 : 0;
+  p1.n_blocks = inter / kTileRows;
+  p1.hidden = h;
+  p1.inter = inter;
+  p1.has_shared_weights = has_shared ? 1 : 0;
+  p1.early_shared_first = c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens);
+  p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
+
+  UmmaParams p2 = p1;
+  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride, 2 * kTileRows);
+  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0, 2 * kTileRows);
+  else p2.map_w_shared = p2.map_w_routed;
+  for (int b = 0; b < 5; ++b) {
+    bad |= make_token_map(&p2.map_tok_routed_box[b], c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b]);
+    if (has_shared) bad |= make_token_map(&p2.map_tok_shared_box[b], c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, kBoxes[b]);
+    else p2.map_tok_shared_box[b] = p2.map_tok_routed_box[b];
+  }
+  if (bad) return false;
+  p2.wsf_routed = static_cast<const int32_t*>(w.w2_sf);
+  p2.wsf_shared = static_cast<const int32_t*>(w.shared_w2_sf);
+  p2.tsf_routed = c.at<int32_t>(c.lay.act_sf);
+  p2.tsf_shared = c.at<int32_t>(c.lay.shared_act_sf);
+  p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
+  p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
+  p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
+  p2.k_dim = inter;
+  p2.rows_per_expert = h;
+  p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
+  p2.n_blocks = h / (2 * kTileRows);
+  out[0] = p1;
+  out[1] = p2;
+  return true;
+}
+
+// the kept record for (workspace, weights, geometry, family), built on first use; least recently used slot is replaced
+const PlanEntry* cached_plan(const Ctx& c, const MmoeWeights& w, bool has_shared) {
+  const PlanKey key = make_key(c, w, has_shared);
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  PlanEntry* victim = &g_plans[0];
+  for (PlanEntry& e : g_plans) {
+    if (e.stamp != 0 && e.key == key) {
+      e.stamp = ++g_plan_clock;
+      return &e;
+    }
+    if (e.stamp < victim->stamp) victim = &e;
+  }
+  const bool ok = c.family == kFamilyWeightsAsA ? build_sa(c, w, has_shared, victim->sa) : build_tm(c, w, has_shared, victim->tm);
+  if (!ok) {
+    victim->stamp = 0;
+    return nullptr;
+  }
+  victim->key = key;
+  victim->stamp = ++g_plan_clock;
+  return victim;
 }
 
 }  // namespace
@@ -697,90 +816,53 @@ int prepare_umma(const MmoeGeometry& geo) {
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m,
                                 cudaStream_t s) {
   if (!tc_ready()) return cudaErrorNotReady;
-  const int h = c.geo.hidden, inter = c.geo.intermediate, el = c.e_local;
-  const int box = box_rows_of(block_m);
   const bool has_shared = c.geo.num_shared_experts > 0 && w.shared_w13 != nullptr && m > 0;
   const int64_t timeout_ns = (o.timeout_ms > 0 ? (int64_t)o.timeout_ms : 2000) * 1000000ll;
-  if (c.family != kFamilyWeightsAsA) return launch_experts_tm(c, w, o, m, has_shared, timeout_ns, s);
-
-  UmmaParams p1{};
-  int bad = 0;
-  bad |= make_w13_map(&p1.map_w_routed, true, w.w13, h, (uint64_t)el * 2 * inter, w.w13_slice_stride);
-  if (has_shared) bad |= make_w13_map(&p1.map_w_shared, false, w.shared_w13, h, 2 * (uint64_t)inter, 0);
-  else p1.map_w_shared = p1.map_w_routed;
-  // token maps: one per box size a tile of this launch can pick (never above the kernel's own box)
-  const uint32_t kBoxes[5] = {16, 32, 64, 80, 128};
-  for (int b = 0; b < 5 && (int)kBoxes[b] <= box; ++b) {
-    bad |= make_token_map(&p1.map_tok_routed_box[b], c.ws + c.lay.pool_x, h, c.lay.pool_rows, kBoxes[b]);
-    if (has_shared) bad |= make_token_map(&p1.map_tok_shared_box[b], c.ws + c.lay.x, h, c.geo.num_max_tokens, kBoxes[b]);
-    else p1.map_tok_shared_box[b] = p1.map_tok_routed_box[b];
-  }
-  if (bad) return cudaErrorInvalidValue;
-  p1.plan = c.ws + c.lay.plan;
-  p1.wsf_routed = static_cast<const int32_t*>(w.w13_sf);
-  p1.wsf_shared = static_cast<const int32_t*>(w.shared_w13_sf);
-  p1.tsf_routed = c.at<int32_t>(c.lay.pool_sf);
-  p1.tsf_shared = c.at<int32_t>(c.lay.shared_x_sf);
-  p1.tsf_rows_routed = c.lay.pool_sf_rows;
-  p1.tsf_rows_shared = c.lay.shared_sf_rows;
-  p1.act_routed = c.at<uint8_t>(c.lay.act_x);
-  p1.act_shared = c.at<uint8_t>(c.lay.shared_act_x);
-  p1.act_sf_routed = c.at<uint8_t>(c.lay.act_sf);
-  p1.act_sf_shared = c.at<uint8_t>(c.lay.shared_act_sf);
-  p1.act_sf_rows_routed = c.lay.pool_sf_rows;
-  p1.act_sf_rows_shared = c.lay.shared_sf_rows;
-  p1.pool_w = c.at<float>(c.lay.pool_w);
-  p1.status = c.at<int32_t>(c.lay.status);
-  p1.timeout_ns = timeout_ns;
-  p1.e_local = el;
-  p1.num_ranks = c.geo.num_ranks;
-  p1.k_dim = h;
-  p1.rows_per_expert = 2 * inter;
-  p1.routed_sliced = w.w13_slice_stride > 0 ? 1 : 0;
-  p1.n_blocks = inter / kTileRows;
-  p1.hidden = h;
-  p1.inter = inter;
-  p1.clamp = o.activation_clamp;
-  p1.fast_math = o.fast_math;
-  p1.has_shared_weights = has_shared ? 1 : 0;
-  p1.tile_select = c.tile_select;
-  p1.early_shared_first = c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens);
-  p1.early_shared_cap = static_cast<int>(shared_tile_capacity(c.geo.num_max_tokens));
-
-  UmmaParams p2 = p1;
-  bad |= make_weight_map(&p2.map_w_routed, true, w.w2, inter, (uint64_t)el * h, w.w2_slice_stride, 2 * kTileRows);
-  if (has_shared) bad |= make_weight_map(&p2.map_w_shared, false, w.shared_w2, inter, (uint64_t)h, 0, 2 * kTileRows);
-  else p2.map_w_shared = p2.map_w_routed;
-  for (int b = 0; b < 5 && (int)kBoxes[b] <= box; ++b) {
-    bad |= make_token_map(&p2.map_tok_routed_box[b], c.ws + c.lay.act_x, inter, c.lay.pool_rows, kBoxes[b]);
-    if (has_shared) bad |= make_token_map(&p2.map_tok_shared_box[b], c.ws + c.lay.shared_act_x, inter, c.geo.num_max_tokens, kBoxes[b]);
-    else p2.map_tok_shared_box[b] = p2.map_tok_routed_box[b];
-  }
-  if (bad) return cudaErrorInvalidValue;
-  p2.wsf_routed = static_cast<const int32_t*>(w.w2_sf);
-  p2.wsf_shared = static_cast<const int32_t*>(w.shared_w2_sf);
-  p2.tsf_routed = c.at<int32_t>(c.lay.act_sf);
-  p2.tsf_shared = c.at<int32_t>(c.lay.shared_act_sf);
-  p2.ret = c.at<__nv_bfloat16>(c.lay.ret);
-  p2.shared_out = c.at<__nv_bfloat16>(c.lay.shared_out);
-  p2.pool_dst = c.at<int32_t>(c.lay.pool_dst);
-  if (c.peer_ws != nullptr && c.geo.num_ranks > 1 && c.tile_select != 2) {
-    p2.fused_return = 1;
-    p2.ep_me = c.geo.rank;
-    p2.ep_totals = reinterpret_cast<const int32_t*>(c.ws + c.lay.ep_sync + ep_totals_offset());
-    for (int r = 0; r < c.geo.num_ranks; ++r)
-      p2.ep_ret_recv[r] = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(const_cast<void*>(c.peer_ws[r])) + c.lay.ret_recv);
-  }
-  p2.k_dim = inter;
-  p2.rows_per_expert = h;
-  p2.routed_sliced = w.w2_slice_stride > 0 ? 1 : 0;
-  p2.n_blocks = h / (2 * kTileRows);
-
+  const PlanEntry* plan = cached_plan(c, w, has_shared);
+  if (plan == nullptr) return cudaErrorInvalidValue;
+  const bool fused = c.peer_ws != nullptr && c.geo.num_ranks > 1 && c.tile_select != 2;
   const int mask = o.layer_mask == 0 ? 3 : o.layer_mask;
   cudaError_t e = cudaSuccess;
-  if (mask & 1) e = launch_layer<1>(p1, box, s);
-  if (e != cudaSuccess) return e;
-  if (mask & 2) e = launch_layer<2>(p2, box, s);
+
+  // what changes from call to call is patched into a copy of the kept parameters
+  auto patch = [&](auto& p, bool layer2) {
+    p.timeout_ns = timeout_ns;
+    p.clamp = o.activation_clamp;
+    p.fast_math = o.fast_math;
+    p.tile_select = c.tile_select;
+    if (layer2 && fused) {
+      p.ep_me = c.geo.rank;
+      p.ep_totals = reinterpret_cast<const int32_t*>(c.ws + c.lay.ep_sync + ep_totals_offset());
+      for (int r = 0; r < c.geo.num_ranks; ++r)
+        p.ep_ret_recv[r] = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(const_cast<void*>(c.peer_ws[r])) + c.lay.ret_recv);
+    }
+  };
+  if (c.family != kFamilyWeightsAsA) {
+    const int ctas = c.family == kFamilyTokensAsAPair ? 2 : 1;
+    if (mask & 1) {
+      TmParams p = plan->tm[0];
+      patch(p, false);
+      e = tm_launch(1, false, ctas, p, s);
+    }
+    if (e == cudaSuccess && (mask & 2)) {
+      TmParams p = plan->tm[1];
+      patch(p, true);
+      e = tm_launch(2, fused, ctas, p, s);
+    }
+    return e;
+  }
+  const int box = box_rows_of(block_m);
+  if (mask & 1) {
+    UmmaParams p = plan->sa[0];
+    patch(p, false);
+    e = launch_layer<1>(p, box, s);
+  }
+  if (e == cudaSuccess && (mask & 2)) {
+    UmmaParams p = plan->sa[1];
+    patch(p, true);
+    p.fused_return = fused ? 1 : 0;
+    e = launch_layer<2>(p, box, s);
+  }
   return e;
 }
 
