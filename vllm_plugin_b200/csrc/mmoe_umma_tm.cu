@@ -62,7 +62,12 @@ struct TmShape {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStagesRaw = (kSmemBudget - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;   // control block + stages + alignment slack
+  static constexpr int kStagingBytes = 4 * 32 * 128;        // layer 2: one 32-row x 128-byte output block per epilogue warp
+  static constexpr int kMainBytes = 1024 + kStages * kStageBytes;          // control block + stages
+  // + staging (layer 2 only: layer 1 leaves the rest of the SM's shared memory to the small kernels that run beside the
+  // shared expert's GEMM1 on the second stream) + alignment slack
+  static constexpr int smem_bytes(int layer) { return kMainBytes + (layer == 2 ? kStagingBytes : 0) + 1024; }
+  static constexpr int kSmemBytes = kMainBytes + kStagingBytes + 1024;
   static constexpr int kAccCols = kTmN;                     // TMEM columns of one accumulator
   static constexpr int kSfCol = 2 * kAccCols;               // scale columns of stage s: [kSfCol + 12 s, + 12)
   static_assert(kStages >= 4, "pipeline depth");
@@ -489,22 +494,42 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
           }
         }
       } else {
+        // Rows leave as 128-byte segments: the warp's 32 x 64 block of BF16 values goes through a swizzled staging block
+        // in shared memory (16-byte chunk c of row r at chunk c ^ (r & 7): conflict-free both ways), then 8 lanes write
+        // one row's 128 contiguous bytes -- four full lines per instruction instead of 32 scattered 16-byte pieces,
+        // which is what matters when the destination is another rank's buffer across NVLink.
+        uint8_t* stg = smem + S::kMainBytes + (warp - 2) * 4096;
+        const int sub = lane >> 3, chunk = lane & 7;
+        // destination of the four rows this lane helps to write in each of the eight steps (row 4j + sub)
+        __nv_bfloat16* dst_row[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const unsigned long long ptr = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out), 4 * j + sub);
+          dst_row[j] = reinterpret_cast<__nv_bfloat16*>(ptr);       // null for rows past the tile's last token
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < blk.n_cols; c0 += 64) {
           uint32_t v[64];
           tc_ld32(d0 + c0, v);
           tc_ld32(d0 + c0 + 32, v + 32);
           tc_ld_wait();
-          uint32_t w[32];
+          __syncwarp();                                   // the previous block has been read out
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(v[2 * c]), __uint_as_float(v[2 * c + 1]));
-            w[c] = *reinterpret_cast<const uint32_t*>(&pr);
+          for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * t]), __uint_as_float(v[8 * c + 2 * t + 1]));
+              w[t] = *reinterpret_cast<const uint32_t*>(&pr);
+            }
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          if (live) {
-            uint4* dst = reinterpret_cast<uint4*>(out + c0);
+          __syncwarp();
 #pragma unroll
-            for (int c = 0; c < 8; ++c) dst[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+          for (int j = 0; j < 8; ++j) {
+            const int r = 4 * j + sub;
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((chunk ^ (r & 7)) << 4));
+            if (dst_row[j] != nullptr) *reinterpret_cast<uint4*>(dst_row[j] + c0 + chunk * 8) = val;
           }
         }
       }
@@ -540,13 +565,13 @@ template <int kLayer, bool kFused, int kCtas>
 cudaError_t tm_launch_one(const TmParams& p, int grid, cudaStream_t s) {
   using S = TmShape<kCtas>;
   if (kCtas == 1) {
-    tm_kernel<kLayer, kFused, 1><<<grid, kTmThreads, S::kSmemBytes, s>>>(p);
+    tm_kernel<kLayer, kFused, 1><<<grid, kTmThreads, S::smem_bytes(kLayer), s>>>(p);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid & ~1);
   cfg.blockDim = dim3(kTmThreads);
-  cfg.dynamicSmemBytes = S::kSmemBytes;
+  cfg.dynamicSmemBytes = S::smem_bytes(kLayer);
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -560,10 +585,10 @@ cudaError_t tm_launch_one(const TmParams& p, int grid, cudaStream_t s) {
 
 template <int kCtas>
 cudaError_t tm_prepare_ctas() {
-  const int bytes = TmShape<kCtas>::kSmemBytes;
-  cudaError_t e = cudaFuncSetAttribute(tm_kernel<1, false, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, false, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, true, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  using S = TmShape<kCtas>;
+  cudaError_t e = cudaFuncSetAttribute(tm_kernel<1, false, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes(1));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, false, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes(2));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(tm_kernel<2, true, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes(2));
   return e;
 }
 
