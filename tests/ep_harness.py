@@ -210,3 +210,116 @@ def layer_body(rank, world, geometry, tokens_per_rank, seed, routing_kw, t_max, 
     if a.numel():
         ulp = torch.pow(2.0, torch.floor(torch.log2(b.abs().clamp(min=2.0 ** -126))) - 7)
         assert float(((a - b).abs() - torch.clamp(ulp, min=2e-2)).max()) <= 0, met
+
+
+def eplb_body(rank, world, token_counts, seed):
+    """Load-balancer geometry of the benchmark's configuration 4 at reduced H / I: 384 logical experts + 8 redundant
+    copies of the 8 hottest ones (from a seeded Zipf(1.2) histogram) = 392 physical experts, top-6, one shared expert.
+    Every token count is captured as a CUDA graph and replayed; then the weights are reloaded IN PLACE under a reshuffled
+    physical -> logical map (addresses unchanged, as the layer class reloads), the routing is re-mapped, and the same
+    graphs are replayed again.  A token's output does not depend on the placement, so the second replay must equal the
+    first bit for bit, and both must match the oracle (cf. tests/eplb_gpu_harness.py:396-562 of the reference)."""
+    import helpers as H
+    from oracle import mmoe_oracle as O
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend.frontend import read_status
+
+    dev = torch.device("cuda", rank)
+    hidden, inter, k, logical_n, redundant = 512, 256, 6, 384, 8
+    physical_n = logical_n + redundant
+    e_l = physical_n // world
+    logical = O.make_experts(logical_n, hidden, inter, seed)
+    shared = O.make_shared_expert(hidden, inter, seed + 1000)
+    g = torch.Generator().manual_seed(seed + 1)
+    pop = 1.0 / torch.arange(1, logical_n + 1, dtype=torch.float32) ** 1.2
+    hist = torch.zeros(logical_n)
+    hist[torch.randperm(logical_n, generator=g)] = pop
+    hottest = torch.topk(hist, redundant).indices.tolist()
+    placements = [list(range(logical_n)) + hottest]                         # physical slot -> logical expert
+    shuffle = torch.randperm(physical_n, generator=g).tolist()
+    placements.append([placements[0][p] for p in shuffle])                  # after the rebalance
+
+    def physical_ids(logical_ids, placement):
+        """Replica choice the engine makes before the layer: copy (token + slot) % copies, slots ascending."""
+        slots = {}
+        for p, l in enumerate(placement):
+            slots.setdefault(l, []).append(p)
+        out = logical_ids.clone()
+        for t in range(logical_ids.shape[0]):
+            for s in range(k):
+                l = int(logical_ids[t, s])
+                if l >= 0:
+                    copies = slots[l]
+                    out[t, s] = copies[(t + s) % len(copies)]
+        return out
+
+    def rank_weights(placement):
+        layer = H.Layer(hidden, inter, physical_n, k, [logical[l] for l in placement], shared)
+        return layer, H.kernel_weights(layer, dev, rank * e_l, (rank + 1) * e_l)
+
+    layer0, (l1, l2, sl1, sl2) = rank_weights(placements[0])
+    buf = api.get_symm_buffer_for_mega_moe(dist.group.WORLD, physical_n, 1920, k, hidden, inter, 1)
+    assert world == 1 or buf.peer_ptrs is not None, "symmetric memory was expected to be available"
+    api.set_kernel_options(ep_transport="peer", fuse_return=True)
+    variants = api.precompile_mega_moe_variants(world, physical_n, 1920, k, hidden, inter, 1)
+    assert set(api.get_block_m_for_mega_moe(world, physical_n, 1920, m, k) for m in token_counts) <= set(variants)
+    stats = torch.zeros(e_l, dtype=torch.int32, device=dev)
+
+    cases = []
+    for j, m in enumerate(token_counts):
+        hid = [O.make_hidden(m, hidden, seed + 100 * j + r) for r in range(world)]
+        routed = [O.make_routing(m, logical_n, k, seed + 100 * j + 50 + r, zipf_s=1.2, mask_frac=0.05) for r in range(world)]
+        cases.append((m, hid, [r_[0] for r_ in routed], [r_[1] for r_ in routed]))
+
+    graphs = []
+    for m, hid, lids, w in cases:
+        ids_d = physical_ids(lids[rank], placements[0]).to(dev)             # updated in place before the second replay
+        hid_d, w_d = hid[rank].to(dev), w[rank].to(dev)
+        y = torch.empty((m, hidden), dtype=torch.bfloat16, device=dev)
+
+        def call(hid_d=hid_d, ids_d=ids_d, w_d=w_d, y=y):
+            api.stage_inputs_for_mega_moe(buf, hid_d, ids_d, w_d)
+            api.fp8_fp4_mega_moe(y, l1, l2, buf, sl1, sl2, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0)
+
+        call()                                                               # warm-up outside capture
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            call()
+        graphs.append((graph, ids_d, y, (hid_d, w_d)))       # the graph reads these buffers at every replay: keep them
+
+    def replay_all(placement):
+        outs = []
+        for (graph, ids_d, y, _inputs), (m, hid, lids, w) in zip(graphs, cases):
+            ids_d.copy_(physical_ids(lids[rank], placement))
+            y.zero_()
+            stats.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph.replay()
+            read_status(buf)
+            phys = [physical_ids(lids[r], placement) for r in range(world)]
+            bm = api.get_block_m_for_mega_moe(world, physical_n, 1920, m, k)
+            plan = O.dispatch_plan(phys, physical_n, rank, bm)
+            assert torch.equal(buf.recv_count.cpu().long(), plan.recv_count), f"receive counts, M={m}"
+            assert torch.equal(stats.cpu().long(), plan.recv_total), f"statistics, M={m}"
+            layer = H.Layer(hidden, inter, physical_n, k, [logical[l] for l in placement], shared)
+            ref = O.moe_layer(hid, phys, w, layer.experts, shared, 10.0, only_ranks=[rank])[rank]
+            met = O.parity_metrics(y.cpu(), ref)
+            assert met["rel_l2"] <= 1e-3, (m, met)
+            outs.append(y.clone())
+        return outs
+
+    first = replay_all(placements[0])
+    # reload in place under the reshuffled map: same tensors, same addresses, new rows
+    _, (n1, n2, _, _) = rank_weights(placements[1])
+    before = (l1[0].data_ptr(), l1[1].data_ptr(), l2[0].data_ptr(), l2[1].data_ptr())
+    for dst, src in ((l1[0], n1[0]), (l1[1], n1[1]), (l2[0], n2[0]), (l2[1], n2[1])):
+        dst.copy_(src)
+    assert before == (l1[0].data_ptr(), l1[1].data_ptr(), l2[0].data_ptr(), l2[1].data_ptr())
+    torch.cuda.synchronize()
+    dist.barrier()
+    second = replay_all(placements[1])
+    for a, b, (m, *_rest) in zip(first, second, cases):
+        assert torch.equal(a, b), f"output changed with the placement at M={m}"

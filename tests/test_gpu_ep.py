@@ -38,3 +38,25 @@ def test_layer_matches_oracle_at_ep(world, tokens, kw, transport, graph):
     CUDA graph) and with the host-driven NCCL exchange."""
     _need(world)
     run_ranks(world, "nccl", layer_body, SMALL, tokens, 3, kw, 1920, transport, graph, timeout=240)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_draft_model_split_top3(world):
+    """Configuration 2 of the benchmark at reduced H / I: E=128, top-3 (16 experts per rank at EP8), capacity 3840 per
+    rank, prefill- and decode-sized calls on different ranks (including a rank without tokens)."""
+    _need(world)
+    geometry = dict(hidden=512, inter=256, num_experts=128, num_topk=3, shared=True)
+    tokens = (300, 1, 32, 7, 130, 64, 0, 255)[:world]
+    run_ranks(world, "nccl", layer_body, geometry, tokens, 9, dict(zipf_s=1.2, mask_frac=0.05, hot=2), 3840, "peer", False,
+              timeout=300)
+    run_ranks(world, "nccl", layer_body, geometry, (32,) * world, 10, {}, 3840, "peer", True, timeout=300)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_redundant_experts_graphs_and_reload_under_a_reshuffled_map(world):
+    """Configuration 4 of the benchmark at reduced H / I: 392 physical experts (384 + copies of the 8 hottest), top-6,
+    decode-sized calls captured and replayed as CUDA graphs, weights reloaded in place under a reshuffled placement,
+    graphs replayed again: bit-identical outputs, oracle parity and bit-exact counts both times."""
+    _need(world)
+    from ep_harness import eplb_body
+    run_ranks(world, "nccl", eplb_body, (1, 4, 16, 64, 256), 17, timeout=420)
