@@ -105,6 +105,20 @@ int mmoe_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidd
                       int32_t ids_are_int64, const float* topk_weights, const uint8_t* is_padding, int32_t num_tokens,
                       int32_t shared_block_m, void* stream);
 
+/* The step in front of kernel (a), fused into the same launch: router top-k + staging.  `router_logits` float
+ * [num_tokens, num_logical_experts]; per token the `num_topk` largest logits are selected (ties: the lower expert id),
+ * the weights are the softmax over the selected logits, and -- with a replica table -- every selected logical expert l
+ * is mapped to its physical copy `replica_slots[l][(token + slot) % replica_count[l]]` (int32 [num_logical_experts] and
+ * [num_logical_experts, max_copies]), the deterministic choice the benchmark's load-balancer configuration prescribes;
+ * without a table the logical id is the physical id.  Ids and weights land in the `topk_idx` / `topk_weights` views
+ * exactly as `mmoe_stage_inputs` would have repacked them; the hidden states are quantised as there.  In the reference
+ * these steps belong to the serving engine in front of the hook (top-k routing and the logical -> physical mapping,
+ * README.md:112-125; patches/vllm-megamoe-plugin.patch:43-69), not to the plugin. */
+int mmoe_route_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidden_bf16, const float* router_logits,
+                            int32_t num_logical_experts, const int32_t* replica_count, const int32_t* replica_slots,
+                            int32_t max_copies, const uint8_t* is_padding, int32_t num_tokens, int32_t shared_block_m,
+                            void* stream);
+
 /* Weights of one rank in the layout `transform_weights_for_mega_moe` produces, which is bit-identical to the
  * reference's (backend/weights.py:120-145): W13 rows interleaved gate/up by 8 ([g0..7, u0..7, g8..15, ...]), scale words
  * in the same row order and 4x32-transposed inside every 128-row block. */

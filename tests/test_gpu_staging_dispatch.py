@@ -132,3 +132,46 @@ def test_dispatch_rejects_out_of_range_expert():
     _dispatch(buf, ids.cuda(), torch.ones((1, 2)).cuda(), 16)
     with pytest.raises(AssertionError):
         read_status(buf)
+
+
+@pytest.mark.parametrize("m,logical,k,replicas", [(1, 384, 6, 0), (37, 384, 6, 8), (500, 128, 3, 16), (260, 64, 8, 0)])
+def test_router_fused_in_front_of_the_quantiser(m, logical, k, replicas):
+    """Top-k by logit (indices bit-exact against torch.topk; Gaussian logits have no ties), softmax over the selected
+    logits (within float32 rounding), the replica choice (token + slot) % copies, and a staged result identical to
+    staging the same ids and weights through the ordinary entry point."""
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend.workspace import SingleRankGroup
+    physical = logical + replicas
+    buf = api.get_symm_buffer_for_mega_moe(SingleRankGroup(), physical, 1920, k, 512, 256, 1)
+    g = torch.Generator().manual_seed(m)
+    logits = torch.randn((m, logical), generator=g)
+    hid = O.make_hidden(m, 512, 3).cuda()
+    replica_map = None
+    ids_ref = torch.topk(logits, k, dim=1).indices
+    w_ref = torch.softmax(torch.topk(logits, k, dim=1).values, dim=1)
+    if replicas:
+        count = torch.ones(logical, dtype=torch.int32)
+        slots = torch.arange(logical, dtype=torch.int32).view(-1, 1).repeat(1, 2)
+        hot = torch.randperm(logical, generator=g)[:replicas]
+        count[hot] = 2
+        slots[hot, 1] = torch.arange(logical, physical, dtype=torch.int32)
+        replica_map = (count.cuda(), slots.cuda())
+        tok = torch.arange(m).view(-1, 1)
+        slot = torch.arange(k).view(1, -1)
+        pick = (tok + slot) % count[ids_ref].long()
+        ids_ref = slots[ids_ref, pick].long()
+    pad = torch.zeros(m, dtype=torch.bool)
+    if m > 3:
+        pad[2] = True
+    bm = api.route_and_stage_inputs_for_mega_moe(buf, hid, logits.cuda(), replica_map=replica_map, is_padding=pad.cuda())
+    torch.cuda.synchronize()
+    got_ids, got_w = buf.topk_idx[:m].cpu(), buf.topk_weights[:m].cpu()
+    want_ids = torch.where(pad.view(-1, 1), torch.full_like(ids_ref, -1), ids_ref)
+    assert torch.equal(got_ids, want_ids)
+    assert torch.allclose(got_w[~pad], w_ref[~pad], rtol=2e-6, atol=1e-7) and float(got_w[pad].abs().sum()) == 0.0
+    staged = (buf.x[:m].view(torch.uint8).clone(), buf.x_sf[:m].clone(), buf.shared_l1_acts_sf.clone())
+    assert api.stage_inputs_for_mega_moe(buf, hid, got_ids.cuda(), got_w.cuda(), is_padding=pad.cuda()) == bm
+    torch.cuda.synchronize()
+    assert torch.equal(buf.x[:m].view(torch.uint8), staged[0]) and torch.equal(buf.x_sf[:m], staged[1])
+    assert torch.equal(buf.shared_l1_acts_sf, staged[2])
+    assert torch.equal(buf.topk_idx[:m].cpu(), want_ids) and torch.equal(buf.topk_weights[:m].cpu(), got_w)

@@ -82,6 +82,16 @@ def stage_inputs_for_mega_moe(sym_buffer, hidden_states, topk_ids, topk_weights,
     return _impl(sym_buffer, hidden_states, topk_ids, topk_weights, is_padding=is_padding, block_m=block_m)
 
 
+def route_and_stage_inputs_for_mega_moe(sym_buffer, hidden_states, router_logits, *, replica_map=None, is_padding=None,
+                                        block_m: Optional[int] = None) -> int:
+    """Router (top-k by logit, softmax over the selected, optional logical -> physical replica choice) fused in front of
+    the input staging: one CUDA launch; returns the BLOCK_M used.  Not part of the reference's surface: there the
+    serving engine routes before it calls the layer."""
+    from .backend.staging import route_and_stage_inputs as _impl
+
+    return _impl(sym_buffer, hidden_states, router_logits, replica_map=replica_map, is_padding=is_padding, block_m=block_m)
+
+
 def precompile_mega_moe_variants(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
                                  hidden: int, intermediate_hidden: int, num_shared_experts: int = 0, *,
                                  activation_clamp: Optional[float] = None, activation_alpha: float = 1.0,
@@ -153,6 +163,7 @@ def __getattr__(name: str):
 __all__ = [
     "get_symm_buffer_for_mega_moe", "transform_weights_for_mega_moe", "fp8_fp4_mega_moe", "get_block_m_for_mega_moe",
     "get_token_alignment_for_mega_moe", "get_unsupported_reason_for_mega_moe", "stage_inputs_for_mega_moe",
+    "route_and_stage_inputs_for_mega_moe",
     "precompile_mega_moe_variants", "set_kernel_options", "get_kernel_options", "is_localization_available",
     "get_balanced_sm_locality_domains", "localize", "localize_mega_moe_weights", "read_status", "SymmBuffer",
 ]

@@ -9,7 +9,7 @@ a Triton kernel and its fallback a torch implementation; here the CUDA kernel is
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -67,6 +67,48 @@ def stage_inputs(sym_buffer, hidden_states: torch.Tensor, topk_ids: torch.Tensor
         ctypes.byref(sym_buffer.geo), sym_buffer.base_ptr, hidden_states.data_ptr(), ids.data_ptr(),
         1 if ids.dtype == torch.int64 else 0, w.data_ptr(), pad_ptr, num_tokens,
         block_m if sym_buffer.num_shared_experts > 0 else 0, _stream_ptr(hidden_states.device)))
+    return block_m
+
+
+def route_and_stage_inputs(sym_buffer, hidden_states: torch.Tensor, router_logits: torch.Tensor, *,
+                           replica_map: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                           is_padding: Optional[torch.Tensor] = None, block_m: Optional[int] = None) -> int:
+    """Router + staging in ONE launch: per token the ``num_topk`` largest ``router_logits`` (ties: the lower expert id),
+    weights = softmax over the selected logits, optional logical -> physical replica choice, then everything
+    :func:`stage_inputs` does.  ``replica_map = (count int32 [L], slots int32 [L, C])``: logical expert ``l`` selected at
+    ``(token, slot)`` goes to ``slots[l, (token + slot) % count[l]]``.  Returns the BLOCK_M used."""
+    num_tokens, hidden_size = hidden_states.shape
+    assert num_tokens <= sym_buffer.num_max_tokens_per_rank, "num_tokens must be <= num_max_tokens_per_rank"
+    if block_m is None:
+        from .frontend import get_block_m_for_mega_moe
+        block_m = get_block_m_for_mega_moe(sym_buffer.num_ranks, sym_buffer.num_experts,
+                                           sym_buffer.num_max_tokens_per_rank, num_tokens, sym_buffer.num_topk,
+                                           sym_buffer.mma_type)
+    if num_tokens == 0:
+        return block_m
+    if hidden_size != sym_buffer.hidden or hidden_states.dtype != torch.bfloat16 or not hidden_states.is_cuda:
+        raise ValueError("MegaMoE input staging requires BF16 CUDA hidden states that match the buffer.")
+    if router_logits.dim() != 2 or router_logits.shape[0] != num_tokens or router_logits.dtype != torch.float32:
+        raise ValueError("MegaMoE routing requires float32 router_logits of shape (num_tokens, num_logical_experts).")
+    hidden_states = hidden_states.contiguous()
+    logits = router_logits.contiguous()
+    count_ptr = slots_ptr = None
+    copies = 0
+    if replica_map is not None:
+        count, slots = replica_map
+        if count.dtype != torch.int32 or slots.dtype != torch.int32 or slots.dim() != 2 or slots.shape[0] != logits.shape[1]:
+            raise ValueError("replica_map must be (count int32 [L], slots int32 [L, C]).")
+        count, slots = count.contiguous(), slots.contiguous()
+        count_ptr, slots_ptr, copies = count.data_ptr(), slots.data_ptr(), slots.shape[1]
+    pad_ptr = None
+    if is_padding is not None:
+        pad = is_padding[:num_tokens].to(torch.uint8).contiguous()
+        pad_ptr = pad.data_ptr()
+    lib = _native.load()
+    _native.check(lib.mmoe_route_stage_inputs(
+        ctypes.byref(sym_buffer.geo), sym_buffer.base_ptr, hidden_states.data_ptr(), logits.data_ptr(), logits.shape[1],
+        count_ptr, slots_ptr, copies, pad_ptr, num_tokens, block_m if sym_buffer.num_shared_experts > 0 else 0,
+        _stream_ptr(hidden_states.device)))
     return block_m
 
 

@@ -304,6 +304,33 @@ int mmoe_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidd
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "stage_inputs launch");
 }
 
+int mmoe_route_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidden_bf16, const float* router_logits,
+                            int32_t num_logical_experts, const int32_t* replica_count, const int32_t* replica_slots,
+                            int32_t max_copies, const uint8_t* is_padding, int32_t num_tokens, int32_t shared_block_m,
+                            void* stream) {
+  mmoe::Ctx c;
+  int rc = make_ctx(geo, workspace, &c);
+  if (rc != MMOE_OK) return rc;
+  rc = check_tokens(geo, num_tokens);
+  if (rc != MMOE_OK) return rc;
+  if (num_logical_experts < geo->num_topk || num_logical_experts > 2048)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "num_logical_experts=%d outside [num_topk, 2048]", num_logical_experts);
+  if ((replica_count == nullptr) != (replica_slots == nullptr) || (replica_count != nullptr && max_copies < 1))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "the replica table needs counts, slots and max_copies >= 1 together");
+  if (replica_count == nullptr && num_logical_experts > geo->num_experts)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "without a replica table logical ids are physical ids: num_logical_experts=%d > num_experts=%d",
+                num_logical_experts, geo->num_experts);
+  if (num_tokens == 0) return MMOE_OK;
+  if (hidden_bf16 == nullptr || router_logits == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "staging inputs must not be NULL");
+  if ((reinterpret_cast<uintptr_t>(hidden_bf16) & 15u) != 0) return fail(MMOE_ERR_INVALID_ARGUMENT, "hidden states must be 16-byte aligned");
+  if (shared_block_m > 0 && !valid_block_m(shared_block_m))
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "shared_block_m=%d is not a BLOCK_M value", shared_block_m);
+  cudaError_t e = mmoe::launch_route_stage(c, hidden_bf16, nullptr, 0, nullptr, router_logits, num_logical_experts, replica_count,
+                                           replica_slots, max_copies, is_padding, num_tokens, shared_block_m,
+                                           static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "route_stage_inputs launch");
+}
+
 int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);

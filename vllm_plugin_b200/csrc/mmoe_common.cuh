@@ -189,6 +189,10 @@ struct Ctx {             // resolved pointers of one call
 
 cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int ids64, const float* w,
                          const uint8_t* pad, int m, int shared_bm, cudaStream_t s);
+cudaError_t launch_route_stage(const Ctx& c, const void* hidden, const void* ids, int ids64, const float* w,
+                               const float* logits, int num_logical, const int32_t* replica_count,
+                               const int32_t* replica_slots, int max_copies, const uint8_t* pad, int m, int shared_bm,
+                               cudaStream_t s);
 cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);

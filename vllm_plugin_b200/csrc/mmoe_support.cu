@@ -62,11 +62,60 @@ __device__ __forceinline__ void stage_vector(const uint4& raw, bool live, int64_
   }
 }
 
+// Router in front of the quantiser (one warp per token): the k largest gate logits (ties: the lower expert id), weights =
+// softmax over the selected logits, and -- when a replica table is given -- the physical copy `(token + slot) % copies`
+// of every selected logical expert, which is the choice a serving engine makes before it calls the layer.
+struct RouterArgs {
+  const float* logits;           // [m, num_logical] or NULL: ids / weights are given and only repacked
+  int num_logical;
+  const int32_t* replica_count;  // [num_logical] or NULL: logical id == physical id
+  const int32_t* replica_slots;  // [num_logical, max_copies]
+  int max_copies;
+};
+
+__device__ void route_token(const RouterArgs& r, int64_t t, int k, bool is_pad, int64_t* __restrict__ ids_out,
+                            float* __restrict__ w_out) {
+  const int lane = threadIdx.x & 31;
+  const float* row = r.logits + t * r.num_logical;
+  uint64_t taken = 0;                               // bit j: this lane's element lane + 32 j has been selected
+  float best_val = 0.f, sum = 0.f;
+  float my_val = 0.f;                               // lane s < k keeps the s-th selection
+  int my_idx = -1;
+  for (int s = 0; s < k; ++s) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int e = lane, j = 0; e < r.num_logical; e += 32, ++j) {
+      const float x = row[e];
+      if (!((taken >> j) & 1ull) && (x > v || (x == v && e < idx))) { v = x; idx = e; }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, d);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, d);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    if ((idx & 31) == lane && idx < r.num_logical) taken |= 1ull << (idx >> 5);
+    if (s == 0) best_val = v;
+    const float ex = expf(v - best_val);
+    sum += ex;
+    if (lane == s) { my_val = ex; my_idx = idx; }
+  }
+  if (lane < k) {
+    int64_t id = my_idx;
+    if (r.replica_count != nullptr && my_idx >= 0 && my_idx < r.num_logical) {
+      const int copies = max(1, r.replica_count[my_idx]);
+      id = r.replica_slots[(int64_t)my_idx * r.max_copies + static_cast<int>((t + lane) % copies)];
+    }
+    ids_out[t * k + lane] = is_pad ? -1 : id;
+    w_out[t * k + lane] = is_pad ? 0.f : __fdiv_rn(my_val, sum);
+  }
+}
+
 __global__ void __launch_bounds__(256) stage_kernel(
     const uint4* __restrict__ hidden, uint2* __restrict__ x_q, int32_t* __restrict__ x_sf,
     int32_t* __restrict__ shared_sf, int64_t shared_rows, int shared_bm,
     const void* __restrict__ ids_in, int ids64, const float* __restrict__ w_in, const uint8_t* __restrict__ pad,
-    int64_t* __restrict__ ids_out, float* __restrict__ w_out, int m, int h, int k) {
+    int64_t* __restrict__ ids_out, float* __restrict__ w_out, int m, int h, int k, RouterArgs router) {
   const int vec_per_row = h / 8;
   const int64_t total = (int64_t)m * vec_per_row;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -88,6 +137,11 @@ __global__ void __launch_bounds__(256) stage_kernel(
     for (int u = 0; u < 4; ++u)
       if (active[u]) stage_vector(raw[u], live[u], i + u * stride, vec_per_row, h, x_q, x_sf, shared_sf, shared_rows, shared_bm);
   }
+  if (router.logits != nullptr) {
+    const int64_t warp = tid >> 5, warps = stride >> 5;
+    for (int64_t t = warp; t < m; t += warps) route_token(router, t, k, pad != nullptr && pad[t] != 0, ids_out, w_out);
+    return;
+  }
   // routing repack (backend/staging.py:244-251)
   const int64_t routes = (int64_t)m * k;
   for (int64_t r = tid; r < routes; r += stride) {
@@ -101,15 +155,23 @@ __global__ void __launch_bounds__(256) stage_kernel(
 
 cudaError_t launch_stage(const Ctx& c, const void* hidden, const void* ids, int ids64, const float* w,
                          const uint8_t* pad, int m, int shared_bm, cudaStream_t s) {
+  return launch_route_stage(c, hidden, ids, ids64, w, nullptr, 0, nullptr, nullptr, 0, pad, m, shared_bm, s);
+}
+
+cudaError_t launch_route_stage(const Ctx& c, const void* hidden, const void* ids, int ids64, const float* w,
+                               const float* logits, int num_logical, const int32_t* replica_count,
+                               const int32_t* replica_slots, int max_copies, const uint8_t* pad, int m, int shared_bm,
+                               cudaStream_t s) {
   if (m == 0) return cudaSuccess;
   const int h = c.geo.hidden;
   const int64_t total = (int64_t)m * h / 8;
   int blocks = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, 148 * 8));
   if (blocks < 1) blocks = 1;
+  const RouterArgs router{logits, num_logical, replica_count, replica_slots, max_copies};
   stage_kernel<<<blocks, 256, 0, s>>>(
       static_cast<const uint4*>(hidden), c.at<uint2>(c.lay.x), c.at<int32_t>(c.lay.x_sf),
       c.at<int32_t>(c.lay.shared_x_sf), c.lay.shared_sf_rows, c.geo.num_shared_experts > 0 ? shared_bm : 0, ids, ids64, w,
-      pad, c.at<int64_t>(c.lay.topk_idx), c.at<float>(c.lay.topk_weights), m, h, c.geo.num_topk);
+      pad, c.at<int64_t>(c.lay.topk_idx), c.at<float>(c.lay.topk_weights), m, h, c.geo.num_topk, router);
   return cudaGetLastError();
 }
 
