@@ -119,6 +119,15 @@ int mmoe_route_stage_inputs(const MmoeGeometry* geo, void* workspace, const void
                             int32_t max_copies, const uint8_t* is_padding, int32_t num_tokens, int32_t shared_block_m,
                             void* stream);
 
+/* NVFP4 activation staging: BF16 `[num_tokens, hidden]` -> packed E2M1 `[num_tokens, hidden/2]` bytes (low nibble = even
+ * K) + one E4M3 scale byte per 16 elements `[num_tokens, hidden/16]`, with the per-tensor `global_scale` of the two-level
+ * NVFP4 recipe: per block s = e4m3_rn(amax * global_scale / 6), q = e2m1_rn(x * global_scale / s); x ~ q * s / global_scale.
+ * The serving engine's hook imports such a call beside the MXFP8 staging (`prepare_megamoe_nvfp4_inputs`,
+ * patches/vllm-megamoe-plugin.patch:10); the reference plugin does not implement it.  Outputs are caller-owned buffers:
+ * the layer's own GEMMs take MXFP8 activations. */
+int mmoe_stage_inputs_nvfp4(const void* hidden_bf16, float global_scale, void* q_out, void* sf_out, int32_t num_tokens,
+                            int32_t hidden, void* stream);
+
 /* Weights of one rank in the layout `transform_weights_for_mega_moe` produces, which is bit-identical to the
  * reference's (backend/weights.py:120-145): W13 rows interleaved gate/up by 8 ([g0..7, u0..7, g8..15, ...]), scale words
  * in the same row order and 4x32-transposed inside every 128-row block. */

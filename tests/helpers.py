@@ -78,7 +78,9 @@ def run_layer(layer: Layer, hidden, ids, w, *, t_max: int = 1920, clamp=10.0, fa
     if weights is None:
         weights = kernel_weights(layer, dev, localized=localized)
     l1, l2, sl1, sl2 = weights
-    api.set_kernel_options(engine=engine, orientation=orientation)
+    from vllm_plugin_b200.backend.frontend import _use_scalar_validation_kernels
+    api.set_kernel_options(orientation=orientation)
+    _use_scalar_validation_kernels(engine == 1)
     try:
         m = hidden.shape[0]
         y = torch.empty((m, layer.hidden), dtype=torch.bfloat16, device=dev)
@@ -89,7 +91,8 @@ def run_layer(layer: Layer, hidden, ids, w, *, t_max: int = 1920, clamp=10.0, fa
         from vllm_plugin_b200.backend.frontend import read_status
         read_status(buf)
     finally:
-        api.set_kernel_options(engine=0, orientation=0)
+        api.set_kernel_options(orientation=0)
+        _use_scalar_validation_kernels(False)
     return y, buf
 
 

@@ -176,6 +176,7 @@ def test_full_size_engines_agree_and_permutation_invariance():
     batch-composition property at full size."""
     from vllm_plugin_b200 import api
     from vllm_plugin_b200.backend.workspace import SingleRankGroup
+    from vllm_plugin_b200.backend.frontend import _use_scalar_validation_kernels
     from vllm_plugin_b200.testing import SyntheticLayer, make_hidden, make_routing
     e, k, h, i, m = 384, 6, 5120, 2304, 256
     syn = SyntheticLayer(h, i, e, True, "cuda", seed=1)
@@ -186,13 +187,13 @@ def test_full_size_engines_agree_and_permutation_invariance():
 
     def run(hh, ii, ww, engine, st=None):
         y = torch.empty((hh.shape[0], h), dtype=torch.bfloat16, device="cuda")
-        api.set_kernel_options(engine=engine)
+        _use_scalar_validation_kernels(engine == 1)
         try:
             api.stage_inputs_for_mega_moe(buf, hh, ii, ww)
             api.fp8_fp4_mega_moe(y, syn.l1, syn.l2, buf, syn.shared_l1, syn.shared_l2,
                                  cumulative_local_expert_recv_stats=st, activation_clamp=10.0)
         finally:
-            api.set_kernel_options(engine=0)
+            _use_scalar_validation_kernels(False)
         from vllm_plugin_b200.backend.frontend import read_status
         read_status(buf)
         return y

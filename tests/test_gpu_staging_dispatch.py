@@ -175,3 +175,21 @@ def test_router_fused_in_front_of_the_quantiser(m, logical, k, replicas):
     assert torch.equal(buf.x[:m].view(torch.uint8), staged[0]) and torch.equal(buf.x_sf[:m], staged[1])
     assert torch.equal(buf.shared_l1_acts_sf, staged[2])
     assert torch.equal(buf.topk_idx[:m].cpu(), want_ids) and torch.equal(buf.topk_weights[:m].cpu(), got_w)
+
+
+@pytest.mark.parametrize("m,h,scale", [(1, 512, 1.0), (77, 5120, 448.0 * 6.0 / 5.0), (300, 1024, 37.5)])
+def test_nvfp4_staging_matches_the_oracle(m, h, scale):
+    """Packed E2M1 bytes and E4M3 block scales bit-exact against the oracle's two-level NVFP4 quantiser, including
+    all-zero blocks, values that saturate the E2M1 grid and exact ties."""
+    from vllm_plugin_b200 import api
+    x = O.make_hidden(m, h, 5).float()
+    x[0, :16] = 0.0                                                   # a zero block: scale 0, values 0
+    if m > 1:
+        x[1, :32] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 4) * (6.0 / scale)   # ties on the grid
+        x[1, 32:48] = 1e4                                             # saturates the block scale
+    x = x.to(torch.bfloat16)
+    q, sf = api.prepare_megamoe_nvfp4_inputs(x.cuda(), scale)
+    torch.cuda.synchronize()
+    q_ref, sf_ref = O.quantize_nvfp4(x, scale)
+    assert torch.equal(sf.cpu(), sf_ref)
+    assert torch.equal(q.cpu(), q_ref)

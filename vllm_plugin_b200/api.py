@@ -92,6 +92,13 @@ def route_and_stage_inputs_for_mega_moe(sym_buffer, hidden_states, router_logits
     return _impl(sym_buffer, hidden_states, router_logits, replica_map=replica_map, is_padding=is_padding, block_m=block_m)
 
 
+def prepare_megamoe_nvfp4_inputs(hidden_states, global_scale: float, out=None):
+    """NVFP4 (E2M1 + E4M3 scale per 16 + per-tensor scale) staging of BF16 hidden states; returns ``(packed, scales)``."""
+    from .backend.staging import prepare_megamoe_nvfp4_inputs as _impl
+
+    return _impl(hidden_states, global_scale, out)
+
+
 def precompile_mega_moe_variants(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
                                  hidden: int, intermediate_hidden: int, num_shared_experts: int = 0, *,
                                  activation_clamp: Optional[float] = None, activation_alpha: float = 1.0,
@@ -163,7 +170,7 @@ def __getattr__(name: str):
 __all__ = [
     "get_symm_buffer_for_mega_moe", "transform_weights_for_mega_moe", "fp8_fp4_mega_moe", "get_block_m_for_mega_moe",
     "get_token_alignment_for_mega_moe", "get_unsupported_reason_for_mega_moe", "stage_inputs_for_mega_moe",
-    "route_and_stage_inputs_for_mega_moe",
+    "route_and_stage_inputs_for_mega_moe", "prepare_megamoe_nvfp4_inputs",
     "precompile_mega_moe_variants", "set_kernel_options", "get_kernel_options", "is_localization_available",
     "get_balanced_sm_locality_domains", "localize", "localize_mega_moe_weights", "read_status", "SymmBuffer",
 ]

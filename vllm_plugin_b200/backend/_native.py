@@ -30,7 +30,7 @@ EXPORTED_SYMBOLS = (
     "mmoe_dispatch_place", "mmoe_experts", "mmoe_combine", "mmoe_forward", "mmoe_read_status", "mmoe_status_string",
     "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc", "mmoe_ep_dispatch", "mmoe_ep_return",
     "mmoe_experts_ep_return", "mmoe_forward_ep", "mmoe_transform_weights",
-    "mmoe_plan_shared", "mmoe_experts_select", "mmoe_route_stage_inputs",
+    "mmoe_plan_shared", "mmoe_experts_select", "mmoe_route_stage_inputs", "mmoe_stage_inputs_nvfp4",
 )
 
 
@@ -86,6 +86,7 @@ def load() -> ctypes.CDLL:
     lib.mmoe_prepare.argtypes = [geo_p, ctypes.POINTER(i32), i32, ctypes.POINTER(i32), vp]
     lib.mmoe_stage_inputs.argtypes = [geo_p, vp, vp, vp, i32, vp, vp, i32, i32, vp]
     lib.mmoe_route_stage_inputs.argtypes = [geo_p, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, vp]
+    lib.mmoe_stage_inputs_nvfp4.argtypes = [vp, ctypes.c_float, vp, vp, i32, i32, vp]
     lib.mmoe_dispatch_count.argtypes = [geo_p, vp, i32, vp]
     lib.mmoe_dispatch_pack.argtypes = [geo_p, vp, i32, vp]
     lib.mmoe_dispatch_place.argtypes = [geo_p, vp, i32, i32, vp, vp]

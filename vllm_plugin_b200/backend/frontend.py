@@ -33,7 +33,6 @@ class KernelOptions:
 
     block_m: int = 0          # > 0 forces the BLOCK_M variant
     timeout_ms: int = 2000    # bound of every device-side wait
-    engine: int = _native.ENGINE_TENSOR_CORE   # ENGINE_SCALAR_VALIDATION selects the scalar validation kernels (tests)
     ep_transport: str = "peer"  # EP > 1: "peer" = device-side exchange over NVLink peer memory (graph-capturable),
                                 # "nccl" = host-driven all-to-allv (also used when symmetric memory is unavailable)
     fuse_return: bool = True    # "peer" transport: GEMM2's epilogue stores its rows straight into the source rank's
@@ -47,6 +46,7 @@ class KernelOptions:
 
 
 _kernel_options = KernelOptions()
+_engine = _native.ENGINE_TENSOR_CORE     # the test-suite may switch to the scalar validation kernels, see below
 _prepared: Dict[Tuple, Tuple[int, ...]] = {}
 
 
@@ -62,6 +62,13 @@ def set_kernel_options(**kwargs: Any) -> KernelOptions:
 
 def get_kernel_options() -> KernelOptions:
     return _kernel_options
+
+
+def _use_scalar_validation_kernels(on: bool) -> None:
+    """Test hook, not an option of the product: run the grouped GEMMs of subsequent calls with the library's scalar
+    validation kernels (plain FP32 dot products over the same plan, pool and epilogues) instead of the tensor-core ones."""
+    global _engine
+    _engine = _native.ENGINE_SCALAR_VALIDATION if on else _native.ENGINE_TENSOR_CORE
 
 
 def require_sm100() -> None:
@@ -305,13 +312,13 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
         assert m <= sym_buffer.num_max_tokens_per_rank, "num_tokens must be <= num_max_tokens_per_rank"
         assert activation_clamp is None or activation_clamp > 0, "activation_clamp must be positive"
     ko = _kernel_options
-    key = (activation_clamp, bool(fast_math), ko.engine, ko.timeout_ms)
+    key = (activation_clamp, bool(fast_math), _engine, ko.timeout_ms)
     if rec.options_key != key:
         rec.options = _native.MmoeOptions(float(activation_clamp) if activation_clamp is not None else math.inf,
-                                          1 if fast_math else 0, ko.engine, ko.timeout_ms)
+                                          1 if fast_math else 0, _engine, ko.timeout_ms)
         rec.options_key = key
     capturing = torch.cuda.is_current_stream_capturing()
-    if not rec.variants_ready and ko.engine == _native.ENGINE_TENSOR_CORE and not capturing:
+    if not rec.variants_ready and _engine == _native.ENGINE_TENSOR_CORE and not capturing:
         precompile_mega_moe_variants(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank,
                                      sym_buffer.num_topk, sym_buffer.hidden, sym_buffer.intermediate_hidden,
                                      sym_buffer.num_shared_experts)

@@ -112,6 +112,27 @@ def route_and_stage_inputs(sym_buffer, hidden_states: torch.Tensor, router_logit
     return block_m
 
 
+def prepare_megamoe_nvfp4_inputs(hidden_states: torch.Tensor, global_scale: float,
+                                 out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """NVFP4 staging of BF16 hidden states (the name the serving engine's hook imports beside the MXFP8 call): returns
+    ``(packed E2M1 uint8 [M, H/2], E4M3 scale bytes uint8 [M, H/16])``; ``global_scale`` is the per-tensor FP32 scale of
+    the two-level recipe (typically ``448 * 6 / amax`` of a calibration pass)."""
+    if hidden_states.dtype != torch.bfloat16 or not hidden_states.is_cuda or hidden_states.dim() != 2:
+        raise ValueError("NVFP4 staging requires 2-D BF16 CUDA hidden states.")
+    m, h = hidden_states.shape
+    if h % 16 != 0:
+        raise ValueError("NVFP4 staging requires hidden_size to be a multiple of 16.")
+    hidden_states = hidden_states.contiguous()
+    if out is None:
+        out = (torch.empty((m, h // 2), dtype=torch.uint8, device=hidden_states.device),
+               torch.empty((m, h // 16), dtype=torch.uint8, device=hidden_states.device))
+    q, sf = out
+    assert q.is_contiguous() and sf.is_contiguous() and q.shape == (m, h // 2) and sf.shape == (m, h // 16)
+    _native.check(_native.load().mmoe_stage_inputs_nvfp4(hidden_states.data_ptr(), float(global_scale), q.data_ptr(),
+                                                         sf.data_ptr(), m, h, _stream_ptr(hidden_states.device)))
+    return q, sf
+
+
 def prepare_megamoe_inputs(hidden_states, topk_weights, topk_ids, sym_buffer, is_padding=None, shared_block_m=None) -> None:
     """Argument order of the serving engine's staging call; the output views are those of ``sym_buffer``."""
     stage_inputs(sym_buffer, hidden_states, topk_ids, topk_weights, is_padding=is_padding, block_m=shared_block_m)

@@ -331,6 +331,19 @@ int mmoe_route_stage_inputs(const MmoeGeometry* geo, void* workspace, const void
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "route_stage_inputs launch");
 }
 
+int mmoe_stage_inputs_nvfp4(const void* hidden_bf16, float global_scale, void* q_out, void* sf_out, int32_t num_tokens,
+                            int32_t hidden, void* stream) {
+  if (num_tokens < 0 || hidden <= 0 || hidden % 16 != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "nvfp4 staging: num_tokens=%d must be >= 0 and hidden=%d a positive multiple of 16", num_tokens, hidden);
+  if (!(global_scale > 0.f) || isinf(global_scale)) return fail(MMOE_ERR_INVALID_ARGUMENT, "nvfp4 staging: global_scale must be positive and finite");
+  if (num_tokens == 0) return MMOE_OK;
+  if (hidden_bf16 == nullptr || q_out == nullptr || sf_out == nullptr) return fail(MMOE_ERR_INVALID_ARGUMENT, "nvfp4 staging: pointers must not be NULL");
+  if ((reinterpret_cast<uintptr_t>(hidden_bf16) & 15u) != 0 || (reinterpret_cast<uintptr_t>(q_out) & 7u) != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "nvfp4 staging: hidden states must be 16-byte and the packed output 8-byte aligned");
+  cudaError_t e = mmoe::launch_stage_nvfp4(hidden_bf16, q_out, sf_out, global_scale, num_tokens, hidden, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "nvfp4 staging launch");
+}
+
 int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_tokens, void* stream) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);

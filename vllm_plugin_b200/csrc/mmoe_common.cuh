@@ -193,6 +193,8 @@ cudaError_t launch_route_stage(const Ctx& c, const void* hidden, const void* ids
                                const float* logits, int num_logical, const int32_t* replica_count,
                                const int32_t* replica_slots, int max_copies, const uint8_t* pad, int m, int shared_bm,
                                cudaStream_t s);
+cudaError_t launch_stage_nvfp4(const void* hidden, void* q_out, void* sf_out, float global_scale, int64_t num_tokens, int hidden_size,
+                               cudaStream_t s);
 cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);

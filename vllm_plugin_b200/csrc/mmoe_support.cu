@@ -3,6 +3,8 @@
 // layout is reproducible run to run.
 #include <algorithm>
 
+#include <cuda_fp4.h>
+
 #include "mmoe_common.cuh"
 
 namespace mmoe {
@@ -172,6 +174,57 @@ cudaError_t launch_route_stage(const Ctx& c, const void* hidden, const void* ids
       static_cast<const uint4*>(hidden), c.at<uint2>(c.lay.x), c.at<int32_t>(c.lay.x_sf),
       c.at<int32_t>(c.lay.shared_x_sf), c.lay.shared_sf_rows, c.geo.num_shared_experts > 0 ? shared_bm : 0, ids, ids64, w,
       pad, c.at<int64_t>(c.lay.topk_idx), c.at<float>(c.lay.topk_weights), m, h, c.geo.num_topk, router);
+  return cudaGetLastError();
+}
+
+// =====================================================================================================================
+// NVFP4 activation staging: BF16 -> packed E2M1 with one E4M3 scale per 16 elements and a per-tensor FP32 scale (the
+// two-level NVFP4 recipe).  The serving engine's hook names such a staging call next to the MXFP8 one
+// (patches/vllm-megamoe-plugin.patch:10, `prepare_megamoe_nvfp4_inputs`); the reference plugin itself never implements
+// it.  Per block of 16:  s = e4m3_rn(amax * global_scale / 6);  q_i = e2m1_rn(x_i * global_scale / s)  (0 when s == 0);
+// x is recovered as q * s / global_scale.  Low nibble = even K, as in the MXFP4 weights.  One thread owns a block (two
+// 16-byte loads, one 8-byte store, one scale byte).
+// =====================================================================================================================
+__global__ void __launch_bounds__(256) stage_nvfp4_kernel(const uint4* __restrict__ hidden, uint2* __restrict__ q_out,
+                                                          uint8_t* __restrict__ sf_out, float global_scale, int64_t blocks16) {
+  for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < blocks16; b += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 raw[2] = {hidden[2 * b], hidden[2 * b + 1]};
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p[j]);
+        v[8 * u + 2 * j] = f.x;
+        v[8 * u + 2 * j + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+    const float s = fminf(__fdiv_rn(__fmul_rn(amax, global_scale), 6.0f), 448.0f);
+    const uint8_t s8 = float_to_e4m3(s);
+    const float sf = e4m3_to_float(s8);
+    const float inv = sf != 0.f ? __fdiv_rn(global_scale, sf) : 0.f;
+    uint32_t w[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(__fmul_rn(v[2 * j], inv), __fmul_rn(v[2 * j + 1], inv)), __NV_E2M1,
+                                                     cudaRoundNearest);
+      w[j >> 2] |= (byte & 0xFFu) << (8 * (j & 3));
+    }
+    q_out[b] = make_uint2(w[0], w[1]);
+    sf_out[b] = s8;
+  }
+}
+
+cudaError_t launch_stage_nvfp4(const void* hidden, void* q_out, void* sf_out, float global_scale, int64_t num_tokens, int hidden_size,
+                               cudaStream_t s) {
+  const int64_t blocks16 = num_tokens * hidden_size / 16;
+  if (blocks16 == 0) return cudaSuccess;
+  const int grid = static_cast<int>(std::min<int64_t>((blocks16 + 255) / 256, 148 * 16));
+  stage_nvfp4_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(hidden), static_cast<uint2*>(q_out),
+                                          static_cast<uint8_t*>(sf_out), global_scale, blocks16);
   return cudaGetLastError();
 }
 
