@@ -172,7 +172,8 @@ int mmoe_dispatch_count(const MmoeGeometry* geo, void* workspace, int32_t num_to
  * which every GPU that loads the library keeps until the process exits.  Limits: num_tokens <= 4096 and
  * num_experts <= 512; larger sizes are rejected with MMOE_ERR_INVALID_ARGUMENT.  This function calls no cudaMalloc,
  * cudaFree or other allocating routine.  The first call on a device looks up the array's device address (the device
- * must be current); make that first call before any stream capture.  All calls on a device share the one array: it
+ * must be current); make that first call before any stream capture (a first call on a capturing stream is refused with
+ * MMOE_ERR_CUDA and launches nothing; host threads may race on the first call).  All calls on a device share the one array: it
  * needs no clearing (every cell read is written first within the call), but two calls that overlap on the GPU (for
  * example on different streams) race on it. */
 int mmoe_route_order_noalloc(const int64_t* topk_idx, int32_t num_tokens, int32_t num_topk, int32_t num_experts,

@@ -2,6 +2,7 @@
 // placement, top-k combine.  All integer work here is deterministic (no order-dependent atomics), so the dispatch
 // layout is reproducible run to run.
 #include <algorithm>
+#include <atomic>
 
 #include <cuda_fp4.h>
 
@@ -390,7 +391,9 @@ static __device__ __align__(256) int32_t g_route_order_scratch[kStaticScratchInt
 
 namespace {
 constexpr int kMaxDevices = 64;
-int32_t* g_scratch_ptr[kMaxDevices] = {};
+// Written by the first call on a device; every writer stores the same address, so the only requirement is that the
+// store and the loads are not torn or reordered: relaxed atomics.
+std::atomic<int32_t*> g_scratch_ptr[kMaxDevices] = {};
 }
 
 cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_experts, int32_t* send_count,
@@ -399,13 +402,19 @@ cudaError_t route_order_static(const int64_t* topk_idx, int m, int k, int num_ex
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-  if (g_scratch_ptr[dev] == nullptr) {           // set-up: first call on this device
+  int32_t* chunk_count = g_scratch_ptr[dev].load(std::memory_order_relaxed);
+  if (chunk_count == nullptr) {                  // set-up: first call on this device
+    // Resolving the symbol may load the module, which a capturing stream forbids: refuse instead of breaking the capture.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(s, &capturing);
+    if (e != cudaSuccess) return e;
+    if (capturing != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_route_order_scratch);
     if (e != cudaSuccess) return e;
-    g_scratch_ptr[dev] = static_cast<int32_t*>(ptr);
+    chunk_count = static_cast<int32_t*>(ptr);
+    g_scratch_ptr[dev].store(chunk_count, std::memory_order_relaxed);
   }
-  int32_t* chunk_count = g_scratch_ptr[dev];
   // nothing in the scratch has to start at zero: pass A overwrites every (chunk, expert) cell that passes B and C read
   const int chunks = std::max(1, (m + kSortChunkTokens - 1) / kSortChunkTokens);
   const size_t smem = (size_t)(kSortChunkTokens * k + num_experts) * sizeof(int32_t);
