@@ -35,9 +35,11 @@ sys.path.insert(0, ROOT)
 H, I, E, K = 5120, 2304, 384, 6
 M_HEADLINE = 3840
 SWEEP = (1, 8, 64, 256, 1024, 2048, 3840)
-# DRAM read + write of a grouped-GEMM1 launch over its algorithmic bytes, from ncu captures of small cases
-# (weights-as-A kernels at E=64 / M=640, tokens-as-A kernels at E=8 / M=640); traffic grows with the experts hit
-NCU_TRAFFIC_RATIO_GEMM1 = {"weights-as-A": 1.049, "tokens-as-A": 1.037}
+# DRAM read + write of the grouped-GEMM1 launches over what they must move (weights and weight scales of the experts
+# hit, FP8 token rows and scales in, FP8 activations and scales out), from ncu captures of small cases: weights-as-A
+# kernels at E=64 / M=640 (867.5 MB measured / 860.8 MB), tokens-as-A kernels at E=8 / M=640 (157.5 / 158.9 MB, the
+# last activation rows still in L2 when the kernel ends).  Both parts grow in proportion to the experts and tokens.
+NCU_TRAFFIC_RATIO_GEMM1 = {"weights-as-A": 1.008, "tokens-as-A": 0.991}
 # tensor pipe rate of `tcgen05.mma.kind::mxf8f6f4.block_scale` measured with back-to-back instructions (M=128, N>=160):
 # 8190 MAC per clock and SM, i.e. the nominal 8192
 TENSOR_MAC_PER_CLK_SM = 8192
@@ -441,9 +443,11 @@ def run_ours(args):
         w2_bytes = distinct_mean * (H * I // 2 + H * I // 32) + (H * I + H * I // 32)
         g1_tflops, g1_gbs = g1_flops / (g1_ms * 1e-3) / 1e12, w13_bytes / (g1_ms * 1e-3) / 1e9
         tensor_bound = g1_flops / (tensor_peak * 1e12) > w13_bytes / (peak_hbm * 1e9)
-        common = {"kernel": kernel_name, "traffic": w13_bytes * NCU_TRAFFIC_RATIO_GEMM1[family],
-                  "traffic_source": "DRAM read+write per algorithmic byte from the ncu capture of a small case of this kernel, "
-                                    "scaled by the experts hit",
+        token_side_bytes = pairs_mean * (H + H // 32 + I + I // 32)     # FP8 rows + scales in, activations + scales out
+        common = {"kernel": kernel_name, "traffic": (w13_bytes + token_side_bytes) * NCU_TRAFFIC_RATIO_GEMM1[family],
+                  "traffic_source": "DRAM read+write over (weight bytes + token rows in + activations out) from the ncu capture "
+                                    "of a small case of this kernel, scaled by the experts hit and the rows processed",
+                  "token_side_bytes_per_launch": token_side_bytes,
                   "algorithmic_bytes_per_launch": w13_bytes, "algorithmic_flops_per_launch": g1_flops, "ms_per_launch": g1_ms}
         if tensor_bound:
             roofline = {"bound": "tensor", "achieved": g1_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
