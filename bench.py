@@ -301,7 +301,7 @@ def run_ours(args):
     # the ordering / placement on a second stream), 2 routed GEMMs, combine = 12 (6 at M <= 128: one fused ordering/plan
     # launch and one launch per GEMM).  The peer exchange adds publish, push, 2 flag waits and a flag kernel (17);
     # its unfused form has one launch per GEMM and a return copy (14); NCCL: the pack kernel, one launch per GEMM (10)
-    launches_per_step = (12 if m > 128 else 6) if world == 1 else {"nccl": 10, "peer-unfused": 14, "peer": 17}[args.ep_transport]
+    launches_per_step = (12 if m > 128 else (6 if m * K > 128 else 5)) if world == 1 else {"nccl": 10, "peer-unfused": 14, "peer": 17}[args.ep_transport]
 
     # ---- eager host cost of one call (staging + layer), microseconds of CPU time per call with nothing to wait for
     torch.cuda.synchronize(dev)

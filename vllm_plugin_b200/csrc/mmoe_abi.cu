@@ -288,6 +288,7 @@ int mmoe_prepare(const MmoeGeometry* geo, int32_t* block_ms, int32_t cap, int32_
 int mmoe_stage_inputs(const MmoeGeometry* geo, void* workspace, const void* hidden_bf16, const void* topk_ids,
                       int32_t ids_are_int64, const float* topk_weights, const uint8_t* is_padding, int32_t num_tokens,
                       int32_t shared_block_m, void* stream) {
+  mmoe::ChainScope chain(num_tokens <= 128);
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);
   if (rc != MMOE_OK) return rc;
@@ -308,6 +309,7 @@ int mmoe_route_stage_inputs(const MmoeGeometry* geo, void* workspace, const void
                             int32_t num_logical_experts, const int32_t* replica_count, const int32_t* replica_slots,
                             int32_t max_copies, const uint8_t* is_padding, int32_t num_tokens, int32_t shared_block_m,
                             void* stream) {
+  mmoe::ChainScope chain(num_tokens <= 128);
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);
   if (rc != MMOE_OK) return rc;
@@ -530,6 +532,7 @@ int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t
 
 int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream) {
+  mmoe::ChainScope chain(num_tokens <= 128);
   if (geo != nullptr && geo->num_ranks != 1)
     return fail(MMOE_ERR_INVALID_ARGUMENT, "mmoe_forward is the single-rank sequence; call mmoe_forward_ep for num_ranks > 1");
   const bool decode = geo != nullptr && num_tokens > 0 && num_tokens <= 128 && geo->num_experts <= 512 &&
@@ -570,12 +573,14 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
   cudaError_t e = cudaEventRecord(lane->fork, main_stream);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(lane->stream, lane->fork, 0);
   if (e != cudaSuccess) return cuda_fail(e, "forking the dispatch stream");
+  mmoe::break_chain();                      // the side stream's first kernel follows an event, not a kernel
   const int rc_side = dispatch(lane->stream);
   e = cudaEventRecord(lane->join, lane->stream);
   rc = mmoe_plan_shared(geo, workspace, num_tokens, block_m, stream);
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 2);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(main_stream, lane->join, 0);
   if (e != cudaSuccess) return cuda_fail(e, "joining the dispatch stream");
+  mmoe::break_chain();                      // the next kernel has two predecessors: launch it without the attribute
   if (rc_side != MMOE_OK) return rc_side;
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 1);
   if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);

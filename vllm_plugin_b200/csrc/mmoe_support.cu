@@ -1,6 +1,8 @@
 // HBM-bound support kernels of the MegaMoE layer for sm_100a: input quantiser, route ordering, pool plan and
 // placement, top-k combine.  All integer work here is deterministic (no order-dependent atomics), so the dispatch
 // layout is reproducible run to run.
+#include <stdlib.h>
+
 #include <algorithm>
 #include <atomic>
 
@@ -9,6 +11,33 @@
 #include "mmoe_common.cuh"
 
 namespace mmoe {
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Host side of the chained (programmatic dependent) launches.  MMOE_DISABLE_CHAINED_LAUNCH=1 in the environment turns
+// the attribute off for the whole process (every launch then waits for the full completion of its predecessor).
+// ---------------------------------------------------------------------------------------------------------------------
+namespace {
+thread_local bool g_break_chain = false;
+thread_local bool g_chain_scope = false;   // inside a ChainScope(true) of this thread
+bool chaining_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("MMOE_DISABLE_CHAINED_LAUNCH");
+    return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+  }();
+  return on;
+}
+}  // namespace
+
+ChainScope::ChainScope(bool on) : saved_(g_chain_scope) { g_chain_scope = on && chaining_enabled(); }
+ChainScope::~ChainScope() { g_chain_scope = saved_; }
+
+void break_chain() { g_break_chain = true; }
+
+bool take_chain_flag() {
+  const bool broken = g_break_chain;
+  g_break_chain = false;
+  return g_chain_scope && !broken;
+}
 
 // =====================================================================================================================
 // Kernel (a): BF16 -> MXFP8 E4M3 with one UE8M0 scale per 32 elements, four scale bytes per int32 word.
@@ -119,6 +148,7 @@ __global__ void __launch_bounds__(256) stage_kernel(
     int32_t* __restrict__ shared_sf, int64_t shared_rows, int shared_bm,
     const void* __restrict__ ids_in, int ids64, const float* __restrict__ w_in, const uint8_t* __restrict__ pad,
     int64_t* __restrict__ ids_out, float* __restrict__ w_out, int m, int h, int k, RouterArgs router) {
+  chain_begin();
   const int vec_per_row = h / 8;
   const int64_t total = (int64_t)m * vec_per_row;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -171,8 +201,7 @@ cudaError_t launch_route_stage(const Ctx& c, const void* hidden, const void* ids
   int blocks = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, 148 * 8));
   if (blocks < 1) blocks = 1;
   const RouterArgs router{logits, num_logical, replica_count, replica_slots, max_copies};
-  stage_kernel<<<blocks, 256, 0, s>>>(
-      static_cast<const uint4*>(hidden), c.at<uint2>(c.lay.x), c.at<int32_t>(c.lay.x_sf),
+  launch_chained(stage_kernel, dim3(blocks), dim3(256), 0, s, static_cast<const uint4*>(hidden), c.at<uint2>(c.lay.x), c.at<int32_t>(c.lay.x_sf),
       c.at<int32_t>(c.lay.shared_x_sf), c.lay.shared_sf_rows, c.geo.num_shared_experts > 0 ? shared_bm : 0, ids, ids64, w,
       pad, c.at<int64_t>(c.lay.topk_idx), c.at<float>(c.lay.topk_weights), m, h, c.geo.num_topk, router);
   return cudaGetLastError();
@@ -303,6 +332,7 @@ constexpr int kSortThreads = 256;
 __global__ void __launch_bounds__(kSortThreads) sort_local_kernel(
     const int64_t* __restrict__ topk_idx, int32_t* __restrict__ route_pos, int32_t* __restrict__ chunk_count,
     int32_t* __restrict__ status, int m, int k, int num_experts) {
+  chain_begin();
   extern __shared__ int32_t sm[];
   int32_t* ids = sm;                                // [chunk routes]
   int32_t* hist = sm + kSortChunkTokens * k;        // [num_experts]
@@ -325,6 +355,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_local_kernel(
 __global__ void __launch_bounds__(1024) sort_scan_kernel(
     int32_t* __restrict__ chunk_count, int32_t* __restrict__ send_count, int32_t* __restrict__ send_offset,
     int32_t* __restrict__ recv_count_if_single, int num_chunks, int num_experts) {
+  chain_begin();
   __shared__ int32_t totals[2048 + 1];
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
     int run = 0;
@@ -347,6 +378,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_place_kernel(
     const int64_t* __restrict__ topk_idx, const int32_t* __restrict__ chunk_base,
     const int32_t* __restrict__ send_offset, int32_t* __restrict__ route_pos, int32_t* __restrict__ sorted_route,
     int m, int k, int num_experts) {
+  chain_begin();
   const int64_t total = (int64_t)m * k;
   for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < total; r += (int64_t)gridDim.x * blockDim.x) {
     const int64_t id = topk_idx[r];
@@ -365,13 +397,13 @@ cudaError_t launch_count_sort(const Ctx& c, int m, cudaStream_t s) {
   const int chunks = max(1, (m + kSortChunkTokens - 1) / kSortChunkTokens);
   int32_t* chunk_count = c.at<int32_t>(c.lay.sort_scratch);
   const size_t smem = (size_t)(kSortChunkTokens * k + e) * sizeof(int32_t);
-  sort_local_kernel<<<chunks, kSortThreads, smem, s>>>(c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos),
+  launch_chained(sort_local_kernel, dim3(chunks), dim3(kSortThreads), smem, s, c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos),
                                                        chunk_count, c.at<int32_t>(c.lay.status), m, k, e);
-  sort_scan_kernel<<<1, 1024, 0, s>>>(chunk_count, c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset),
+  launch_chained(sort_scan_kernel, dim3(1), dim3(1024), 0, s, chunk_count, c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset),
                                       c.geo.num_ranks == 1 ? c.at<int32_t>(c.lay.recv_count) : nullptr, chunks, e);
   if (m > 0) {
     const int blocks = static_cast<int>(std::min<int64_t>(((int64_t)m * k + kSortThreads - 1) / kSortThreads, 148 * 8));
-    sort_place_kernel<<<blocks, kSortThreads, 0, s>>>(c.at<int64_t>(c.lay.topk_idx), chunk_count,
+    launch_chained(sort_place_kernel, dim3(blocks), dim3(kSortThreads), 0, s, c.at<int64_t>(c.lay.topk_idx), chunk_count,
                                                       c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.route_pos),
                                                       c.at<int32_t>(c.lay.sorted_route), m, k, e);
   }
@@ -499,11 +531,17 @@ __device__ int emit_shared_tiles(Tile* out, int n, int block_m, int cap, bool pa
 // expert; for CTA pairs into an even number of them (the last may be empty), so that tiles 2j and 2j + 1 of the table
 // always belong to the same expert.  The scale chunks of the pool are this library's own: tile j of the expert uses chunk j of the
 // chunks reserved for the expert's blocks.
+__device__ __forceinline__ void tile_cut(int n, int cap, bool pair, int* parts_out, int* step_out) {
+  const int parts = pair ? 2 * ((n + 2 * cap - 1) / (2 * cap)) : (n + cap - 1) / cap;
+  *parts_out = parts;
+  *step_out = parts == 1 ? n : ((n + parts - 1) / parts + 15) & ~15;
+}
+
 __device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_m, int cap, bool pair, int first_block,
                           bool write) {
   if (n <= 0) return 0;
-  const int parts = pair ? 2 * ((n + 2 * cap - 1) / (2 * cap)) : (n + cap - 1) / cap;
-  const int step = parts == 1 ? n : ((n + parts - 1) / parts + 15) & ~15;
+  int parts, step;
+  tile_cut(n, cap, pair, &parts, &step);
   if (write) {
     const int chunk0 = first_block * chunks_per_block(block_m);
     for (int j = 0; j < parts; ++j)
@@ -516,6 +554,7 @@ __device__ int emit_tiles(Tile* out, int expert, int row_base, int n, int block_
 // experts' receive counts are known: written at the tail of the tile table, counted in the header.
 __global__ void shared_plan_kernel(char* __restrict__ plan_base, int e_local, int num_ranks, int m, int block_m,
                                    int cap, int pair, int64_t first_tile) {
+  chain_begin();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     PlanView pv = plan_view(plan_base, e_local, num_ranks);
     pv.hdr->num_early_shared_tiles = emit_shared_tiles(pv.tiles + first_tile, m, block_m, cap, pair != 0);
@@ -525,6 +564,7 @@ __global__ void shared_plan_kernel(char* __restrict__ plan_base, int e_local, in
 __global__ void __launch_bounds__(1024) plan_kernel(
     char* __restrict__ plan_base, const int32_t* __restrict__ recv_count, int32_t* __restrict__ stats, int e_local,
     int num_ranks, int block_m, int cap, int pair, int m, int has_shared) {
+  chain_begin();
   PlanView pv = plan_view(plan_base, e_local, num_ranks);
   __shared__ int32_t s_blocks[513], s_tiles[513];
   // per-source totals -> rank offsets in receive order
@@ -586,11 +626,25 @@ __global__ void __launch_bounds__(1024) plan_kernel(
 // Decode path at EP1 (one chunk of at most 128 tokens): route ordering and pool plan in ONE single-block launch
 // instead of four, because at a handful of tokens the layer is bound by launch latency.  Same results as
 // sort_local/scan/place + plan_kernel (tested against them).
+// Placement arguments of route_plan_small_kernel (pool_x == nullptr: the placement kernel follows as its own launch)
+struct SmallPlace {
+  const uint4* src_x;
+  const int32_t* src_sf;
+  const float* src_w;
+  uint4* pool_x;
+  int32_t* pool_sf;
+  float* pool_w;
+  int32_t* pool_dst;
+  int64_t pool_sf_rows;
+  int h;
+};
+
 __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     const int64_t* __restrict__ topk_idx, int32_t* __restrict__ route_pos, int32_t* __restrict__ sorted_route,
     int32_t* __restrict__ send_count, int32_t* __restrict__ send_offset, int32_t* __restrict__ recv_count,
     char* __restrict__ plan_base, int32_t* __restrict__ stats, int32_t* __restrict__ status, int m, int k,
-    int num_experts, int block_m, int cap, int pair, int has_shared) {
+    int num_experts, int block_m, int cap, int pair, int has_shared, SmallPlace place) {
+  chain_begin();
   extern __shared__ int32_t sm[];
   int32_t* ids = sm;                              // [m*k]
   int32_t* hist = sm + kSortChunkTokens * k;      // [E]
@@ -661,6 +715,40 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(
     pv.expert_block_off[num_experts] = boff[num_experts];
     pv.expert_tile_off[num_experts] = toff[num_experts];
   }
+  // A handful of routes: this block also places them (one warp per route), which saves the placement launch.  Route i
+  // of expert e with rank r among the expert's routes is pool row boff[e] * block_m + r, row r - j * step of the
+  // expert's tile j (the cut emit_tiles makes).
+  if (place.pool_x != nullptr) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int vec = place.h / 16, words = place.h / kTileK;
+    for (int i = warp; i < n; i += warps) {
+      if (rank[i] < 0) continue;
+      const int e = ids[i], r = rank[i];
+      int parts, step;
+      tile_cut(hist[e], cap, pair != 0, &parts, &step);
+      const int j = r / step;
+      const int p = boff[e] * block_m + r;
+      const int64_t src_row = i / k;
+      const uint4* src = place.src_x + src_row * vec;
+      uint4* dst = place.pool_x + (int64_t)p * vec;
+      for (int v0 = lane; v0 < vec; v0 += 128) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + 32 * u < vec) q[u] = src[v0 + 32 * u];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + 32 * u < vec) dst[v0 + 32 * u] = q[u];
+      }
+      const int pos = (boff[e] * chunks_per_block(block_m) + j) * kChunkRows + chunk_pos(r - j * step);
+      for (int wd = lane; wd < words; wd += 32)
+        place.pool_sf[(int64_t)wd * place.pool_sf_rows + pos] = place.src_sf[src_row * words + wd];
+      if (lane == 0) {
+        place.pool_w[p] = place.src_w[i];
+        place.pool_dst[p] = off[e] + r;
+      }
+    }
+  }
 }
 
 // Place: one warp per pool row of every routed tile: copy the FP8 row, scatter its scale words into the chunk layout,
@@ -672,6 +760,7 @@ __global__ void __launch_bounds__(256) place_kernel(
     const float* __restrict__ src_w, const int32_t* __restrict__ sorted_route, uint4* __restrict__ pool_x,
     int32_t* __restrict__ pool_sf, float* __restrict__ pool_w, int32_t* __restrict__ pool_dst, int64_t pool_sf_rows,
     int e_local, int num_ranks, int h, int k, int direct) {
+  chain_begin();
   PlanView pv = plan_view(plan_base, e_local, num_ranks);
   const int ntiles = pv.hdr->num_routed_tiles;
   const int block_m = pv.hdr->block_m;
@@ -725,37 +814,43 @@ __global__ void __launch_bounds__(256) place_kernel(
   }
 }
 
-// EP1, M <= 128: fused route ordering + plan, then placement
+// EP1, M <= 128: fused route ordering + plan; up to 128 routes the same block also places them, beyond that the
+// placement kernel follows
 cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {
   const int k = c.geo.num_topk, e = c.geo.num_experts;
   const size_t smem = (size_t)(2 * kSortChunkTokens * k + 6 * e + 3) * sizeof(int32_t);
-  route_plan_small_kernel<<<1, 1024, smem, s>>>(
-      c.at<int64_t>(c.lay.topk_idx), c.at<int32_t>(c.lay.route_pos), c.at<int32_t>(c.lay.sorted_route),
-      c.at<int32_t>(c.lay.send_count), c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.recv_count),
-      c.ws + c.lay.plan, stats, c.at<int32_t>(c.lay.status), m, k, e, block_m, tile_cap(block_m, c.family),
-      c.family == kFamilyTokensAsAPair, c.geo.num_shared_experts > 0);
-  place_kernel<<<148 * 2, 256, 0, s>>>(
-      c.ws + c.lay.plan, c.at<uint4>(c.lay.x), c.at<int32_t>(c.lay.x_sf), c.at<float>(c.lay.topk_weights),
-      c.at<int32_t>(c.lay.sorted_route), c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf),
-      c.at<float>(c.lay.pool_w), c.at<int32_t>(c.lay.pool_dst), c.lay.pool_sf_rows, c.e_local, 1, c.geo.hidden,
-      c.geo.num_topk, 1);
+  const bool place_here = m * k <= 128;
+  SmallPlace place = {};
+  if (place_here)
+    place = SmallPlace{c.at<uint4>(c.lay.x), c.at<int32_t>(c.lay.x_sf), c.at<float>(c.lay.topk_weights),
+                       c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf), c.at<float>(c.lay.pool_w),
+                       c.at<int32_t>(c.lay.pool_dst), c.lay.pool_sf_rows, c.geo.hidden};
+  launch_chained(route_plan_small_kernel, dim3(1), dim3(1024), smem, s, c.at<int64_t>(c.lay.topk_idx),
+                 c.at<int32_t>(c.lay.route_pos), c.at<int32_t>(c.lay.sorted_route), c.at<int32_t>(c.lay.send_count),
+                 c.at<int32_t>(c.lay.send_offset), c.at<int32_t>(c.lay.recv_count), c.ws + c.lay.plan, stats,
+                 c.at<int32_t>(c.lay.status), m, k, e, block_m, tile_cap(block_m, c.family),
+                 c.family == kFamilyTokensAsAPair, c.geo.num_shared_experts > 0, place);
+  if (!place_here)
+    launch_chained(place_kernel, dim3(148 * 2), dim3(256), 0, s, c.ws + c.lay.plan, c.at<uint4>(c.lay.x),
+                   c.at<int32_t>(c.lay.x_sf), c.at<float>(c.lay.topk_weights), c.at<int32_t>(c.lay.sorted_route),
+                   c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf), c.at<float>(c.lay.pool_w),
+                   c.at<int32_t>(c.lay.pool_dst), c.lay.pool_sf_rows, c.e_local, 1, c.geo.hidden, c.geo.num_topk, 1);
   return cudaGetLastError();
 }
 
 cudaError_t launch_shared_plan(const Ctx& c, int m, int block_m, cudaStream_t s) {
-  shared_plan_kernel<<<1, 32, 0, s>>>(c.ws + c.lay.plan, c.e_local, c.geo.num_ranks, m, block_m,
+  launch_chained(shared_plan_kernel, dim3(1), dim3(32), 0, s, c.ws + c.lay.plan, c.e_local, c.geo.num_ranks, m, block_m,
                                       tile_cap(block_m, c.family), c.family == kFamilyTokensAsAPair, c.lay.max_tiles - shared_tile_capacity(c.geo.num_max_tokens));
   return cudaGetLastError();
 }
 
 cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s) {
   const int R = c.geo.num_ranks;
-  plan_kernel<<<1, 1024, 0, s>>>(c.ws + c.lay.plan, c.at<int32_t>(c.lay.recv_count), stats, c.e_local, R, block_m,
+  launch_chained(plan_kernel, dim3(1), dim3(1024), 0, s, c.ws + c.lay.plan, c.at<int32_t>(c.lay.recv_count), stats, c.e_local, R, block_m,
                                  tile_cap(block_m, c.family), c.family == kFamilyTokensAsAPair, m,
                                  c.geo.num_shared_experts > 0);
   const bool direct = R == 1;
-  place_kernel<<<148 * 8, 256, 0, s>>>(
-      c.ws + c.lay.plan, direct ? c.at<uint4>(c.lay.x) : c.at<uint4>(c.lay.recv_x),
+  launch_chained(place_kernel, dim3(148 * 8), dim3(256), 0, s, c.ws + c.lay.plan, direct ? c.at<uint4>(c.lay.x) : c.at<uint4>(c.lay.recv_x),
       direct ? c.at<int32_t>(c.lay.x_sf) : c.at<int32_t>(c.lay.recv_sf),
       direct ? c.at<float>(c.lay.topk_weights) : c.at<float>(c.lay.recv_w), c.at<int32_t>(c.lay.sorted_route),
       c.at<uint4>(c.lay.pool_x), c.at<int32_t>(c.lay.pool_sf), c.at<float>(c.lay.pool_w), c.at<int32_t>(c.lay.pool_dst),
@@ -780,6 +875,7 @@ __device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
 __global__ void __launch_bounds__(256) combine_kernel(
     const uint4* __restrict__ rows, const int32_t* __restrict__ route_pos, const uint4* __restrict__ shared_out,
     uint4* __restrict__ y, int m, int h, int k) {
+  chain_begin();
   const int vec = h / 8;
   const int64_t total = (int64_t)m * vec;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -804,7 +900,7 @@ cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s) {
   const int64_t total = (int64_t)m * c.geo.hidden / 8;
   const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
   const uint4* rows = c.geo.num_ranks == 1 ? c.at<uint4>(c.lay.ret) : c.at<uint4>(c.lay.ret_recv);
-  combine_kernel<<<blocks, 256, 0, s>>>(rows, c.at<int32_t>(c.lay.route_pos),
+  launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, s, rows, c.at<int32_t>(c.lay.route_pos),
                                         c.geo.num_shared_experts > 0 ? c.at<uint4>(c.lay.shared_out) : nullptr,
                                         static_cast<uint4*>(y), m, c.geo.hidden, c.geo.num_topk);
   return cudaGetLastError();

@@ -140,14 +140,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
   uint8_t* sf_base = b_base + S::kStages * S::kBBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
-  const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
-  const int num_tiles = p.tile_select == 2
-                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
-                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
-  const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
-  const int k_stages = p.k_dim / kTileK;
-  const uint32_t num_stages = static_cast<uint32_t>(p.num_stages);
+  chain_release();
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S::kStages; ++i) {
@@ -161,6 +154,15 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // Everything above touches only this CTA's own shared and tensor memory, so it may run while the kernel before this
+  // one in the stream is still running; everything below reads what that kernel wrote.
+  chain_wait();
   if (kFused) {
     if (threadIdx.x == 0) ctl->out_base[32] = p.shared_out;
     {
@@ -178,16 +180,18 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
       }
     }
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
+  const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
+  const int num_tiles = p.tile_select == 2
+                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
+                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
+  const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
+  const int k_stages = p.k_dim / kTileK;
+  const uint32_t num_stages = static_cast<uint32_t>(p.num_stages);
 
   Waiter waiter{&ctl->abort_flag, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), kLayer, warp};
 
@@ -517,8 +521,10 @@ cudaError_t launch_one(const UmmaParams& p0, cudaStream_t s) {
   UmmaParams p = p0;
   p.num_stages = g_tune_stages > 0 && g_tune_stages < S::kStages ? g_tune_stages : S::kStages;
   const int grid = tc_num_sms();
-  if (kLayer == 2 && p.fused_return) umma_kernel<2, kBoxRows, true><<<grid, kThreads, Shape<2, kBoxRows>::kSmemBytes, s>>>(p);
-  else umma_kernel<kLayer, kBoxRows, false><<<grid, kThreads, S::kSmemBytes, s>>>(p);
+  if (kLayer == 2 && p.fused_return)
+    launch_chained(umma_kernel<2, kBoxRows, true>, dim3(grid), dim3(kThreads), Shape<2, kBoxRows>::kSmemBytes, s, p);
+  else
+    launch_chained(umma_kernel<kLayer, kBoxRows, false>, dim3(grid), dim3(kThreads), S::kSmemBytes, s, p);
   return cudaGetLastError();
 }
 

@@ -207,19 +207,7 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
   const uint32_t cta = kCtas == 2 ? cluster_ctarank() : 0u;      // 0 = leader
   const bool leader = cta == 0;
   const int unit = blockIdx.x / kCtas, num_units = gridDim.x / kCtas;   // a unit = one CTA or one CTA pair
-  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
-  const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
-  const int num_tiles = p.tile_select == 2
-                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
-                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
-  const int half = p.rows_per_expert / 2;
-  const int blocks_per_half = (half + kTmN - 1) / kTmN;
-  const int n_blocks = 2 * blocks_per_half;
-  // a pair plan holds an even number of tiles per expert: tiles 2j and 2j + 1 form pair j
-  const int64_t num_tasks = (int64_t)(num_tiles / kCtas) * n_blocks;
-  const int k_stages = p.k_dim / kTileK;
-  // tile record of task `t` for this CTA
-  auto tile_of = [&](int64_t t) -> Tile { return tiles[(t / n_blocks) * kCtas + cta]; };
+  chain_release();
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S::kStages; ++i) {
@@ -236,6 +224,18 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 1) {       // the same warp of both CTAs of a pair allocates
+    if (kCtas == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+  }
+  // Everything above touches only this CTA's own shared and tensor memory, so it may run while the kernel before this
+  // one in the stream is still running; everything below reads what that kernel wrote.
+  chain_wait();
   if (kFused) {
     const int t = threadIdx.x - 32;
     if (t >= 0 && t < p.num_ranks) {
@@ -250,20 +250,24 @@ __global__ void __launch_bounds__(kTmThreads, 1) tm_kernel(const __grid_constant
       ctl->rank_off[p.num_ranks] = run;
     }
   }
-  if (warp == 1) {       // the same warp of both CTAs of a pair allocates
-    if (kCtas == 1) {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-  }
   tc_fence_before();
   __syncthreads();
   if (kCtas == 2) cluster_sync_all();       // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
+  const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
+  const int num_tiles = p.tile_select == 2
+                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
+                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
+  const int half = p.rows_per_expert / 2;
+  const int blocks_per_half = (half + kTmN - 1) / kTmN;
+  const int n_blocks = 2 * blocks_per_half;
+  // a pair plan holds an even number of tiles per expert: tiles 2j and 2j + 1 form pair j
+  const int64_t num_tasks = (int64_t)(num_tiles / kCtas) * n_blocks;
+  const int k_stages = p.k_dim / kTileK;
+  // tile record of task `t` for this CTA
+  auto tile_of = [&](int64_t t) -> Tile { return tiles[(t / n_blocks) * kCtas + cta]; };
 
   Waiter waiter{&ctl->abort_flag, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), 20 + kLayer, warp};
   const uint32_t tile_full0 = smem_u32(&ctl->tile_full[0]), sf_full0 = smem_u32(&ctl->sf_full[0]);
@@ -565,8 +569,7 @@ template <int kLayer, bool kFused, int kCtas>
 cudaError_t tm_launch_one(const TmParams& p, int grid, cudaStream_t s) {
   using S = TmShape<kCtas>;
   if (kCtas == 1) {
-    tm_kernel<kLayer, kFused, 1><<<grid, kTmThreads, S::smem_bytes(kLayer), s>>>(p);
-    return cudaGetLastError();
+    return launch_chained(tm_kernel<kLayer, kFused, 1>, dim3(grid), dim3(kTmThreads), S::smem_bytes(kLayer), s, p);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid & ~1);
