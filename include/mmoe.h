@@ -222,7 +222,10 @@ int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void*
 int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream);
 /* EP1 convenience: count, place, experts, combine.  Past the decode sizes (num_tokens > 128, with a shared expert) the
  * routed experts' ordering, plan and placement run on the library's second stream while the shared expert's GEMMs run
- * on `stream` (fork / join with events, capturable); same result as the separate calls. */
+ * on `stream` (fork / join with events, capturable); same result as the separate calls.  Up to 128 tokens the call is
+ * one stream and five or six launches: one block orders the routes, builds the plan and (up to 128 routes) places the
+ * rows; the kernels are launched as a programmatic chain, so that each one's launch and set-up overlap its
+ * predecessor (MMOE_DISABLE_CHAINED_LAUNCH=1 in the environment, read once per process: ordinary launches). */
 int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream);
 

@@ -96,3 +96,46 @@ def test_headline_geometry_against_the_oracle(layer384, m):
     ref = H.oracle_token_sample(hid, ids, w, sample, lambda e: H.synthetic_expert(syn, e), H.synthetic_shared(syn))
     H.log_parity(f"E=384 M={m} block_m={bm}", H.strict_metrics(y[sample.cuda()], ref))
     assert_parity(y[sample.cuda()], ref, f"E=384 M={m}")
+
+
+@pytest.mark.parametrize("m,bm", [(1, 16), (8, 16), (21, 16), (100, 16), (30, 32), (128, 32)])
+def test_small_call_path_equals_the_general_sequence(layer16, m, bm):
+    """Calls of at most 128 tokens order the routes and build the plan in one block (which, up to 128 routes, also
+    places the rows) and launch their kernels as a programmatic chain.  Every intermediate and the output must equal,
+    bit for bit, what the general sequence leaves: three ordering passes, plan, placement, GEMMs, combine."""
+    import ctypes
+    from vllm_plugin_b200 import api
+    from vllm_plugin_b200.backend import _native
+    from vllm_plugin_b200.backend.frontend import _weights_struct, check_mega_moe_arguments, read_status
+    from vllm_plugin_b200.testing import make_hidden, make_routing
+    syn, buf = layer16
+    hid = make_hidden(m, HID, 31 + m, "cuda")
+    ids, w = make_routing(m, 16, 6, 32 + m, "cuda", zipf_s=1.2, mask_frac=0.05)
+    api.set_kernel_options(block_m=bm, orientation=1)
+    try:
+        y_one = _run(syn, buf, hid, ids, w)
+        pool_one = buf.l1_acts.view(torch.uint8).clone()
+        act_one = buf.l2_acts.view(torch.uint8).clone()
+        ret_one = buf.ret.view(torch.int16).clone()
+        y = torch.empty_like(y_one)
+        s13, s2 = check_mega_moe_arguments(y, syn.l1, syn.l2, buf, syn.shared_l1, syn.shared_l2, None, (1, 1, 32),
+                                           "swiglu", 10.0, True, 1.0, 0.0)
+        ws = _weights_struct(syn.l1, syn.l2, syn.shared_l1, syn.shared_l2, s13, s2)
+        lib = _native.load()
+        geo, base = ctypes.byref(buf.geo), buf.base_ptr
+        sp = torch.cuda.current_stream().cuda_stream
+        api.stage_inputs_for_mega_moe(buf, hid, ids, w, block_m=bm)
+        _native.check(lib.mmoe_dispatch_count(geo, base, m, sp))
+        _native.check(lib.mmoe_dispatch_place(geo, base, m, bm, None, sp))
+        for mask in (1, 2):
+            opts = _native.MmoeOptions(10.0, 1, 0, 2000, mask)
+            _native.check(lib.mmoe_experts(geo, base, ctypes.byref(ws), ctypes.byref(opts), m, bm, sp))
+        _native.check(lib.mmoe_combine(geo, base, y.data_ptr(), m, sp))
+        read_status(buf)
+    finally:
+        api.set_kernel_options(block_m=0, orientation=0)
+    # rows of the pool that hold no route are never written by either sequence: compare the regions whole
+    assert torch.equal(buf.l1_acts.view(torch.uint8), pool_one), "placed rows"
+    assert torch.equal(buf.l2_acts.view(torch.uint8), act_one), "SwiGLU output of the routed experts"
+    assert torch.equal(buf.ret.view(torch.int16), ret_one), "expert output rows"
+    assert torch.equal(y, y_one)

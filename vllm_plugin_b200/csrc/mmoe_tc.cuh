@@ -167,6 +167,20 @@ struct Waiter {
     if ((threadIdx.x & 31) == 0) ok = wait(bar, parity);
     return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
   }
+  // true when the call is being abandoned: another role gave up, or this wait has used up the budget (recorded)
+  __device__ __forceinline__ bool abandoned() {
+    if (*abort_flag != 0) return true;
+    if (global_timer() > deadline) {
+      *abort_flag = 1;
+      if (atomicCAS(&status[kStatusTimeout], 0, 1) == 0) {
+        status[kStatusKernel] = kernel_id;
+        status[kStatusRole] = role;
+        status[kStatusBlock] = static_cast<int32_t>(blockIdx.x);
+      }
+      return true;
+    }
+    return false;
+  }
   // true when the phase completed, false when the call is being abandoned
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
     // one non-blocking probe first: a hardware-suspended wait wakes up late, and that latency lands on the critical
@@ -174,18 +188,7 @@ struct Waiter {
     if (mbar_test_wait(bar, parity)) return true;
     for (uint32_t spin = 0;; ++spin) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((spin & 63u) == 63u) {
-        if (*abort_flag != 0) return false;
-        if (global_timer() > deadline) {
-          *abort_flag = 1;
-          if (atomicCAS(&status[kStatusTimeout], 0, 1) == 0) {
-            status[kStatusKernel] = kernel_id;
-            status[kStatusRole] = role;
-            status[kStatusBlock] = static_cast<int32_t>(blockIdx.x);
-          }
-          return false;
-        }
-      }
+      if ((spin & 63u) == 63u && abandoned()) return false;
     }
   }
 };

@@ -125,25 +125,324 @@ struct Shape {
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
+// ---------------------------------------------------------------------------------------------------------------
+// The roles, each a function of (layer, largest token box, stage layout L).
+// ---------------------------------------------------------------------------------------------------------------
+struct RoleState {                 // pipeline position of a role
+  uint32_t stage = 0, phase = 0;   // position in the shared-memory ring
+  uint32_t it = 0;                 // tasks this CTA has started: selects the accumulator buffer and its barrier phase
+  bool ok = true;                  // false once the call is being abandoned
+};
+
+struct Cta {                       // where a role finds the CTA's resources
+  Control* ctl;
+  uint8_t* a_base;
+  uint8_t* b_base;
+  uint8_t* sf_base;
+  uint32_t tmem_base;
+  uint32_t num_stages;
+};
+
+struct TaskList {
+  const Tile* tiles;
+  int64_t num_tasks;
+};
+
+__device__ __forceinline__ TaskList task_list(const UmmaParams& p) {
+  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
+  const int num_tiles = p.tile_select == 2
+                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
+                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
+  return TaskList{pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0), (int64_t)num_tiles * p.n_blocks};
+}
+
+// ------------------------------------------------------------------------------------------------ producer
+// One thread.  Everything that does not change inside a task is computed once per task; the K loop only bumps 32-bit
+// coordinates and two pointers, because a one-thread loop runs at instruction latency, not throughput.
+template <int kLayer, int kBoxRows, typename L>
+__device__ __forceinline__ void sa_producer(const UmmaParams& p, const Cta& c, const TaskList& tl, Waiter& waiter,
+                                            RoleState& st) {
+  constexpr bool kInPlace = kLayer == 1 && kBoxRows == 32;
+  const int k_stages = p.k_dim / kTileK;
+  const uint32_t full0 = smem_u32(&c.ctl->full[0]), empty0 = smem_u32(&c.ctl->empty[0]);
+  const uint32_t a0 = smem_u32(c.a_base), b0 = smem_u32(c.b_base), sf0 = smem_u32(c.sf_base);
+  for (int64_t task = blockIdx.x; task < tl.num_tasks && st.ok; task += gridDim.x) {
+    const int tile_idx = static_cast<int>(task / p.n_blocks);
+    const int nb = static_cast<int>(task - (int64_t)tile_idx * p.n_blocks);
+    const Tile tile = tl.tiles[tile_idx];
+    const bool shared = tile.expert == kSharedExpert;
+    // smallest token box that covers the tile (16 / 32 / 64 / 128 rows): fewer rows to move and to pad
+    const int n16 = (tile.n_valid + 15) & ~15;
+    const int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : (n16 <= 80 ? 3 : 4)));   // never above kBoxRows
+    const uint32_t box_rows = box_sel == 3 ? 80u : (box_sel == 4 ? 128u : (16u << box_sel));
+    const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
+    const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
+    const int e = shared ? 0 : tile.expert;
+    // The 256 stored weight rows of the task.  Layer 1 reads W13 in its stored order [g0..7, u0..7, g8..15, ...]
+    // through a 5-D map (K, row in group of 8, group of 16 rows, gate/up, slice): one box of 8 x 16 x 2 lands the
+    // 128 gate rows and then the 128 up rows of 128 consecutive channels.  Layer 2 reads 256 consecutive rows.
+    const bool sliced = !shared && p.routed_sliced != 0;
+    const int rows_slice = sliced ? p.rows_per_expert / 2 : p.rows_per_expert;   // rows of one expert in one slice
+    const int r0 = 2 * nb * kTileRows;                                           // first stored row of the task
+    const int slice = sliced ? r0 / rows_slice : 0;
+    const int row = e * rows_slice + r0 % rows_slice;
+    const int group = row / 16;
+    const int32_t* wsf = (shared ? p.wsf_shared : p.wsf_routed) + (int64_t)e * k_stages * p.rows_per_expert + r0;
+    const int64_t tsf_rows = shared ? p.tsf_rows_shared : p.tsf_rows_routed;
+    const int32_t* tsf = (shared ? p.tsf_shared : p.tsf_routed) + (int64_t)tile.sf_chunk * kChunkRows;
+    const uint32_t a_tx = shared ? 2 * kTileRows * kTileK : kTileRows * kTileK;   // packed FP4 counts its global bytes
+    const uint32_t tx = a_tx + box_rows * kTileK + 1024 + 512;
+    int k0 = 0;
+    for (int kb = 0; kb < k_stages; ++kb, k0 += kTileK, wsf += p.rows_per_expert, tsf += tsf_rows) {
+      if (!waiter.wait(empty0 + 8 * st.stage, st.phase ^ 1u)) { st.ok = false; break; }
+      const uint32_t bar = full0 + 8 * st.stage;
+      mbar_expect_tx(bar, tx);
+      const uint32_t a_dst = a0 + st.stage * L::kABytes;
+      const uint32_t sf_dst = sf0 + st.stage * L::kSfBytes;
+      if (kLayer == 1) tma_load_5d(a_dst, wmap, k0, 0, group, 0, slice, bar);
+      else tma_load_3d(a_dst, wmap, k0, row, slice, bar);
+      // layer 1: raw scales of the 256 stored rows, permuted by the MMA warps; layer 2: two chunks already in order
+      bulk_load(sf_dst + (kLayer == 1 && !kInPlace ? 3 * 512 : 0), wsf, 1024, bar);
+      tma_load_2d(b0 + st.stage * L::kBBytes, tmap, k0, tile.row0, bar);
+      bulk_load(sf_dst + 2 * 512, tsf, 512, bar);
+      if (++st.stage == c.num_stages) { st.stage = 0; st.phase ^= 1u; }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ MMA issuers
+// Two warps, one per weight tile / accumulator (h = 0, 1).  The whole warp walks the loop so that loop state stays
+// warp-uniform; one elected lane issues.  Each warp copies the scales it needs into its own TMEM columns, so no
+// ordering between the two warps' tensor-core instructions is needed.
+// Layer 1 first rearranges its tile's weight scales: the stored W13 scales follow the stored row order (gate/up
+// interleaved by 8, then the 4x32 transpose inside each 128-row block), the accumulator wants the scales of 128 gate
+// (h = 0) or up (h = 1) channels in tensor-memory order; each lane moves 4 of the 128 words.
+template <int kLayer, int kBoxRows, typename L>
+__device__ __forceinline__ void sa_mma(const UmmaParams& p, const Cta& c, const TaskList& tl, Waiter& waiter,
+                                       RoleState& st, int h) {
+  constexpr bool kInPlace = kLayer == 1 && kBoxRows == 32;
+  const int lane = threadIdx.x & 31;
+  const int k_stages = p.k_dim / kTileK;
+  const uint32_t ready0 = smem_u32(&c.ctl->full[0]);
+  const uint32_t empty0 = smem_u32(&c.ctl->empty[0]);
+  const uint64_t sw128_hi = desc_hi_sw128();
+  const uint64_t sf_hi = desc_hi_sf(128);
+  // layer 1: the four 8-row groups of a weight tile's scales sit 256 bytes apart (see the rearrangement below)
+  const uint64_t sfa_hi = kInPlace ? desc_hi_sf(256) : sf_hi;
+  const uint32_t a_lo0 = ((smem_u32(c.a_base) & 0x3FFFFu) >> 4) + h * (kTileRows * kTileK >> 4);
+  const uint32_t b_lo0 = (smem_u32(c.b_base) & 0x3FFFFu) >> 4;
+  const uint32_t sf_lo0 = (smem_u32(c.sf_base) & 0x3FFFFu) >> 4;
+  const uint32_t sfa_col = c.tmem_base + L::kSfCol + 4 * h;
+  const uint32_t sfb_col = c.tmem_base + L::kSfCol + 8 + 4 * h;
+  int src[4];                                    // layer 1: source word of the 4 destination words this lane writes
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int q = lane + 32 * t;                 // destination position inside the 128-word block
+    const int m = 32 * (q & 3) + (q >> 2);       // channel of the tile that position serves
+    const int r = 16 * ((m & 63) >> 3) + 8 * h + (m & 7);   // stored row inside its 128-row block
+    src[t] = 128 * (m >> 6) + 4 * (r & 31) + (r >> 5);
+  }
+  for (int64_t task = blockIdx.x; task < tl.num_tasks && st.ok; task += gridDim.x, ++st.it) {
+    const Tile tile = tl.tiles[task / p.n_blocks];
+    const bool shared = tile.expert == kSharedExpert;
+    const uint32_t acc_stage = st.it & 1u, acc_phase = (st.it >> 1) & 1u;
+    if (!waiter.wait_warp(smem_u32(&c.ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { st.ok = false; break; }
+    tc_fence_after();
+    const uint32_t n = static_cast<uint32_t>((tile.n_valid + 15) & ~15);
+    const uint32_t idesc0 = make_idesc(shared ? 0u : 5u, 0u, n, 0);
+    const uint32_t d = c.tmem_base + acc_stage * L::kAccCols + h * L::kNCap;
+    const uint32_t sfb = sfb_col + tile.sf_col;
+    for (int kb = 0; kb < k_stages; ++kb) {
+      if (!waiter.wait_warp(ready0 + 8 * st.stage, st.phase)) { st.ok = false; break; }
+      const uint32_t a_lo = a_lo0 + st.stage * (L::kABytes >> 4);
+      const uint32_t b_lo = b_lo0 + st.stage * (L::kBBytes >> 4);
+      const uint32_t sf_lo = sf_lo0 + st.stage * (L::kSfBytes >> 4);
+      if (kLayer == 1 && !kInPlace) {
+        uint32_t* out = reinterpret_cast<uint32_t*>(c.sf_base + st.stage * L::kSfBytes) + 128 * h;
+        const uint32_t* in = reinterpret_cast<const uint32_t*>(c.sf_base + st.stage * L::kSfBytes) + 3 * 128;
+        uint32_t v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) v[t] = in[src[t]];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) out[lane + 32 * t] = v[t];
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to tcgen05.cp
+        __syncwarp();
+      }
+      if (kInPlace) {
+        // In stored order the scale words of the gate rows (h = 0) occupy words [64b, 64b + 32) of the 256-word
+        // area (b = 0..3) and those of the up rows (h = 1) words [64b + 32, 64b + 64): the 128 words a warp reads
+        // are exactly the 128 it may overwrite, so the two warps never touch each other's words.  The rearranged
+        // tile is four 128-byte groups of 8 rows, 256 bytes apart, which is what the copy descriptor describes.
+        uint32_t* area = reinterpret_cast<uint32_t*>(c.sf_base + st.stage * L::kSfBytes);
+        uint32_t v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) v[t] = area[src[t]];
+        __syncwarp();                                                  // every lane has read before any lane writes
+#pragma unroll
+        for (int t = 0; t < 4; ++t) area[64 * t + 32 * h + lane] = v[t];
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+      }
+      if (elect_one()) {
+        tc_cp_sf(sfa_col, sfa_hi | (sf_lo + (kInPlace ? 8 : 32) * h));
+        tc_cp_sf(sfb_col, sf_hi | (sf_lo + 64));
+#pragma unroll
+        for (int k = 0; k < kTileK / 32; ++k)
+          tc_mma(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
+                 idesc0 + k * ((1u << 4) | (1u << 29)),               // scale byte k of both operands
+                 sfa_col, sfb, (kb | k) != 0 ? 1u : 0u);
+        tc_commit(empty0 + 8 * st.stage);            // shared memory of this stage is free once these MMAs retire
+      }
+      __syncwarp();
+      if (++st.stage == c.num_stages) { st.stage = 0; st.phase ^= 1u; }
+    }
+    if (st.ok && elect_one()) tc_commit(smem_u32(&c.ctl->tmem_full[acc_stage]));
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ epilogue
+// Four warps; a thread owns one weight row (accumulator lane), the columns are the tile's tokens.
 // kFused (layer 2, EP > 1): every output row goes to the rank its token came from; compiled as kernels of its own so
 // that the single-destination epilogue of the other cases keeps its shorter inner loop.
-template <int kLayer, int kBoxRows, bool kFused = false>
-__global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant__ UmmaParams p) {
-  static_assert(!kFused || kLayer == 2, "only GEMM2 writes rows back");
-  using S = Shape<kLayer, kBoxRows>;
-  extern __shared__ uint8_t smem_raw[];
+template <int kLayer, int kBoxRows, typename L, bool kFused>
+__device__ __forceinline__ void sa_epilogue(const UmmaParams& p, const Cta& c, const TaskList& tl, Waiter& waiter,
+                                            RoleState& st) {
+  Control* ctl = c.ctl;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+  const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+  for (int64_t task = blockIdx.x; task < tl.num_tasks && st.ok; task += gridDim.x, ++st.it) {
+    const Tile tile = tl.tiles[task / p.n_blocks];
+    const int nb = static_cast<int>(task % p.n_blocks);
+    const bool shared = tile.expert == kSharedExpert;
+    const uint32_t acc_stage = st.it & 1u, acc_phase = (st.it >> 1) & 1u;
+    // Per-token side data of the tile (top-k weight / destination row), one coalesced load per 32 tokens issued
+    // before the accumulator is awaited; tokens read it by shuffle.
+    float wv[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    int dv[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int i = 32 * cc + lane;
+      if (i < tile.n_valid) {
+        if (kLayer == 1) { if (!shared) wv[cc] = __ldg(p.pool_w + tile.row0 + i); }
+        else if (!kFused) dv[cc] = shared ? tile.row0 + i : __ldg(p.pool_dst + tile.row0 + i);
+        else if (shared) dv[cc] = static_cast<int>((32u << kOutSlotShift) | static_cast<uint32_t>(tile.row0 + i));
+        else {
+          const int r = __ldg(p.pool_dst + tile.row0 + i);       // receive-order row
+          int sr = 0;
+          while (sr + 1 < p.num_ranks && r >= ctl->rank_off[sr + 1]) ++sr;
+          dv[cc] = static_cast<int>((static_cast<uint32_t>(sr) << kOutSlotShift) |
+                                    static_cast<uint32_t>(ctl->home_base[sr] + r - ctl->rank_off[sr]));
+        }
+      }
+    }
+    if (!waiter.wait_warp(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { st.ok = false; break; }
+    tc_fence_after();
+    const uint32_t d0 = c.tmem_base + lane_sel + acc_stage * L::kAccCols;
+    const int n16 = (tile.n_valid + 15) & ~15;
+    if (kLayer == 1) {
+      const int row = nb * kTileRows + q * 32 + lane;       // channel
+      uint8_t* act = shared ? p.act_shared : p.act_routed;
+      uint8_t* act_sf = shared ? p.act_sf_shared : p.act_sf_routed;
+      const int64_t sf_rows = shared ? p.act_sf_rows_shared : p.act_sf_rows_routed;
+      // scale byte of (token i, channel group nb*4+q): word nb of the chunk row, byte q
+      uint8_t* sf_out = act_sf + ((int64_t)nb * sf_rows + (int64_t)tile.sf_chunk * kChunkRows) * 4 + q;
+      uint8_t* act_col = act + (int64_t)tile.row0 * p.inter + row;
+      for (int i0 = 0; i0 < n16; i0 += 16) {
+        uint32_t g[16], u[16];
+        tc_ld16(d0 + i0, g);
+        tc_ld16(d0 + L::kNCap + i0, u);
+        tc_ld_wait();
+        const int cc = i0 >> 5;
+        const float wcur = cc == 0 ? wv[0] : (cc == 1 ? wv[1] : (cc == 2 ? wv[2] : wv[3]));
+        int my_sf = 0;
+        // branch-free over the 16 columns so that their dependency chains interleave (the fast-math choice is made
+        // once per batch, not per element); padding columns compute garbage that is never stored
+        auto batch = [&](auto fast) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float wt = __shfl_sync(0xffffffffu, wcur, (i0 & 16) + j);
+            const float a = swiglu_act_t<decltype(fast)::value>(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp);
+            const float amax = warp_max_nonneg(fabsf(a));
+            const int sf_exp = ue8m0_exp_of_amax(amax);
+            g[j] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
+            if (lane == j) my_sf = sf_exp;
+          }
+        };
+        if (p.fast_math != 0) batch(std::true_type{});
+        else batch(std::false_type{});
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (i0 + j < tile.n_valid) act_col[(int64_t)(i0 + j) * p.inter] = static_cast<uint8_t>(g[j]);
+        if (lane < 16 && i0 + lane < tile.n_valid)
+          sf_out[chunk_pos(tile.sf_col * 32 + i0 + lane) * 4] = static_cast<uint8_t>(my_sf);
+      }
+    } else if (!kFused) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = nb * 2 * kTileRows + h * kTileRows + q * 32 + lane;     // output feature
+        __nv_bfloat16* out = (shared ? p.shared_out : p.ret) + row;
+        for (int i0 = 0; i0 < n16; i0 += 16) {
+          uint32_t v[16];
+          tc_ld16(d0 + h * L::kNCap + i0, v);
+          tc_ld_wait();
+          const int cc = i0 >> 5;
+          const int dcur = cc == 0 ? dv[0] : (cc == 1 ? dv[1] : (cc == 2 ? dv[2] : dv[3]));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int dst = __shfl_sync(0xffffffffu, dcur, (i0 & 16) + j);
+            if (i0 + j < tile.n_valid) out[(int64_t)dst * p.hidden] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          }
+        }
+      }
+    } else {
+      // one destination per token: resolve the 16 row pointers of a batch once, use them for both weight blocks
+      const int row0 = nb * 2 * kTileRows + q * 32 + lane;                      // output feature of weight block 0
+      for (int i0 = 0; i0 < n16; i0 += 16) {
+        uint32_t v0[16], v1[16];
+        tc_ld16(d0 + i0, v0);
+        tc_ld16(d0 + L::kNCap + i0, v1);
+        const int cc = i0 >> 5;
+        const int dcur = cc == 0 ? dv[0] : (cc == 1 ? dv[1] : (cc == 2 ? dv[2] : dv[3]));
+        tc_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t dst = static_cast<uint32_t>(__shfl_sync(0xffffffffu, dcur, (i0 & 16) + j));
+          if (i0 + j < tile.n_valid) {
+            __nv_bfloat16* out = ctl->out_base[dst >> kOutSlotShift] +
+                                 (int64_t)(dst & ((1u << kOutSlotShift) - 1u)) * p.hidden + row0;
+            out[0] = __float2bfloat16_rn(__uint_as_float(v0[j]));
+            out[kTileRows] = __float2bfloat16_rn(__uint_as_float(v1[j]));
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    mbar_arrive(smem_u32(&ctl->tmem_empty[acc_stage]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ set-up / teardown
+template <typename L>
+__device__ __forceinline__ Cta sa_carve(uint8_t* smem_raw) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-  Control* ctl = reinterpret_cast<Control*>(smem);
-  uint8_t* a_base = smem + 1024;
-  uint8_t* b_base = a_base + S::kStages * S::kABytes;
-  uint8_t* sf_base = b_base + S::kStages * S::kBBytes;
+  Cta c;
+  c.ctl = reinterpret_cast<Control*>(smem);
+  c.a_base = smem + 1024;
+  c.b_base = c.a_base + L::kStages * L::kABytes;
+  c.sf_base = c.b_base + L::kStages * L::kBBytes;
+  c.tmem_base = 0;
+  c.num_stages = L::kStages;
+  return c;
+}
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  chain_release();
-
+// barriers and tensor memory: touches only this CTA's own shared / tensor memory
+template <typename L>
+__device__ __forceinline__ void sa_setup(Control* ctl) {
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S::kStages; ++i) {
+    for (int i = 0; i < L::kStages; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
       mbar_init(smem_u32(&ctl->empty[i]), 2);          // both MMA warps release a stage
     }
@@ -154,307 +453,15 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if ((threadIdx.x >> 5) == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // Everything above touches only this CTA's own shared and tensor memory, so it may run while the kernel before this
-  // one in the stream is still running; everything below reads what that kernel wrote.
-  chain_wait();
-  if (kFused) {
-    if (threadIdx.x == 0) ctl->out_base[32] = p.shared_out;
-    {
-      const int t = threadIdx.x - 32;
-      if (t >= 0 && t < p.num_ranks) {
-        ctl->out_base[t] = p.ep_ret_recv[t];
-        int b = 0;
-        for (int d = 0; d < p.ep_me; ++d) b += p.ep_totals[t * 32 + d];
-        ctl->home_base[t] = b;
-      }
-      if (threadIdx.x == 64) {
-        int run = 0;
-        for (int sr = 0; sr < p.num_ranks; ++sr) { ctl->rank_off[sr] = run; run += p.ep_totals[sr * 32 + p.ep_me]; }
-        ctl->rank_off[p.num_ranks] = run;
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = ctl->tmem_base;
-  PlanView pv = plan_view(const_cast<char*>(p.plan), p.e_local, p.num_ranks);
-  const Tile* tiles = pv.tiles + (p.tile_select == 2 ? p.early_shared_first : 0);
-  const int num_tiles = p.tile_select == 2
-                            ? (p.has_shared_weights ? max(0, min(pv.hdr->num_early_shared_tiles, p.early_shared_cap)) : 0)
-                            : pv.hdr->num_routed_tiles + (p.tile_select == 0 && p.has_shared_weights ? pv.hdr->num_shared_tiles : 0);
-  const int64_t num_tasks = (int64_t)num_tiles * p.n_blocks;
-  const int k_stages = p.k_dim / kTileK;
-  const uint32_t num_stages = static_cast<uint32_t>(p.num_stages);
+}
 
-  Waiter waiter{&ctl->abort_flag, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), kLayer, warp};
-
-  if (warp == 0) {
-    // ------------------------------------------------------------------------------------------------ producer
-    // One thread.  Everything that does not change inside a task is computed once per task; the K loop only bumps
-    // 32-bit coordinates and two pointers, because a one-thread loop runs at instruction latency, not throughput.
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
-      const uint32_t a0 = smem_u32(a_base), b0 = smem_u32(b_base), sf0 = smem_u32(sf_base);
-      bool ok = true;
-      for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x) {
-        const int tile_idx = static_cast<int>(task / p.n_blocks);
-        const int nb = static_cast<int>(task - (int64_t)tile_idx * p.n_blocks);
-        const Tile tile = tiles[tile_idx];
-        const bool shared = tile.expert == kSharedExpert;
-        // smallest token box that covers the tile (16 / 32 / 64 / 128 rows): fewer rows to move and to pad
-        const int n16 = (tile.n_valid + 15) & ~15;
-        const int box_sel = n16 <= 16 ? 0 : (n16 <= 32 ? 1 : (n16 <= 64 ? 2 : (n16 <= 80 ? 3 : 4)));   // never above kBoxRows
-        const uint32_t box_rows = box_sel == 3 ? 80u : (box_sel == 4 ? 128u : (16u << box_sel));
-        const CUtensorMap* wmap = shared ? &p.map_w_shared : &p.map_w_routed;
-        const CUtensorMap* tmap = shared ? &p.map_tok_shared_box[box_sel] : &p.map_tok_routed_box[box_sel];
-        const int e = shared ? 0 : tile.expert;
-        // The 256 stored weight rows of the task.  Layer 1 reads W13 in its stored order [g0..7, u0..7, g8..15, ...]
-        // through a 5-D map (K, row in group of 8, group of 16 rows, gate/up, slice): one box of 8 x 16 x 2 lands the
-        // 128 gate rows and then the 128 up rows of 128 consecutive channels.  Layer 2 reads 256 consecutive rows.
-        const bool sliced = !shared && p.routed_sliced != 0;
-        const int rows_slice = sliced ? p.rows_per_expert / 2 : p.rows_per_expert;   // rows of one expert in one slice
-        const int r0 = 2 * nb * kTileRows;                                           // first stored row of the task
-        const int slice = sliced ? r0 / rows_slice : 0;
-        const int row = e * rows_slice + r0 % rows_slice;
-        const int group = row / 16;
-        const int32_t* wsf = (shared ? p.wsf_shared : p.wsf_routed) + (int64_t)e * k_stages * p.rows_per_expert + r0;
-        const int64_t tsf_rows = shared ? p.tsf_rows_shared : p.tsf_rows_routed;
-        const int32_t* tsf = (shared ? p.tsf_shared : p.tsf_routed) + (int64_t)tile.sf_chunk * kChunkRows;
-        const uint32_t a_tx = shared ? 2 * kTileRows * kTileK : kTileRows * kTileK;   // packed FP4 counts its global bytes
-        const uint32_t tx = a_tx + box_rows * kTileK + 1024 + 512;
-        int k0 = 0;
-        for (int kb = 0; kb < k_stages; ++kb, k0 += kTileK, wsf += p.rows_per_expert, tsf += tsf_rows) {
-          if (!waiter.wait(empty0 + 8 * stage, phase ^ 1u)) { ok = false; break; }
-          const uint32_t bar = full0 + 8 * stage;
-          mbar_expect_tx(bar, tx);
-          const uint32_t a_dst = a0 + stage * S::kABytes;
-          const uint32_t sf_dst = sf0 + stage * S::kSfBytes;
-          if (kLayer == 1) tma_load_5d(a_dst, wmap, k0, 0, group, 0, slice, bar);
-          else tma_load_3d(a_dst, wmap, k0, row, slice, bar);
-          // layer 1: raw scales of the 256 stored rows, permuted by the MMA warps; layer 2: two chunks already in order
-          bulk_load(sf_dst + (kLayer == 1 && !S::kSfInPlace ? 3 * 512 : 0), wsf, 1024, bar);
-          tma_load_2d(b0 + stage * S::kBBytes, tmap, k0, tile.row0, bar);
-          bulk_load(sf_dst + 2 * 512, tsf, 512, bar);
-          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-  } else if (warp == 1 || warp == 6) {
-    // ------------------------------------------------------------------------------------------------ MMA issuers
-    // Two warps, one per weight tile / accumulator (h = 0, 1).  The whole warp walks the loop so that loop state
-    // stays warp-uniform; one elected lane issues.  Each warp copies the scales it needs into its own TMEM columns,
-    // so no ordering between the two warps' tensor-core instructions is needed.
-    // Layer 1 first rearranges its tile's weight scales: the stored W13 scales follow the stored row order (gate/up
-    // interleaved by 8, then the 4x32 transpose inside each 128-row block), the accumulator wants the scales of 128
-    // gate (h = 0) or up (h = 1) channels in tensor-memory order; each lane moves 4 of the 128 words.
-    {
-      const int h = warp == 1 ? 0 : 1;
-      uint32_t stage = 0, phase = 0;
-      uint32_t it = 0;
-      bool ok = true;
-      const uint32_t ready0 = smem_u32(&ctl->full[0]);
-      const uint32_t empty0 = smem_u32(&ctl->empty[0]);
-      const uint64_t sw128_hi = desc_hi_sw128();
-      const uint64_t sf_hi = desc_hi_sf(128);
-      // layer 1: the four 8-row groups of a weight tile's scales sit 256 bytes apart (see the rearrangement below)
-      const uint64_t sfa_hi = S::kSfInPlace ? desc_hi_sf(256) : sf_hi;
-      const uint32_t a_lo0 = ((smem_u32(a_base) & 0x3FFFFu) >> 4) + h * (kTileRows * kTileK >> 4);
-      const uint32_t b_lo0 = (smem_u32(b_base) & 0x3FFFFu) >> 4;
-      const uint32_t sf_lo0 = (smem_u32(sf_base) & 0x3FFFFu) >> 4;
-      const uint32_t sfa_col = tmem_base + S::kSfCol + 4 * h;
-      const uint32_t sfb_col = tmem_base + S::kSfCol + 8 + 4 * h;
-      int src[4];                                    // layer 1: source word of the 4 destination words this lane writes
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int q = lane + 32 * t;                 // destination position inside the 128-word block
-        const int m = 32 * (q & 3) + (q >> 2);       // channel of the tile that position serves
-        const int r = 16 * ((m & 63) >> 3) + 8 * h + (m & 7);   // stored row inside its 128-row block
-        src[t] = 128 * (m >> 6) + 4 * (r & 31) + (r >> 5);
-      }
-      for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
-        const Tile tile = tiles[task / p.n_blocks];
-        const bool shared = tile.expert == kSharedExpert;
-        const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
-        if (!waiter.wait_warp(smem_u32(&ctl->tmem_empty[acc_stage]), acc_phase ^ 1u)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t n = static_cast<uint32_t>((tile.n_valid + 15) & ~15);
-        const uint32_t idesc0 = make_idesc(shared ? 0u : 5u, 0u, n, 0);
-        const uint32_t d = tmem_base + acc_stage * S::kAccCols + h * S::kNCap;
-        const uint32_t sfb = sfb_col + tile.sf_col;
-        for (int kb = 0; kb < k_stages; ++kb) {
-          if (!waiter.wait_warp(ready0 + 8 * stage, phase)) { ok = false; break; }
-          const uint32_t a_lo = a_lo0 + stage * (S::kABytes >> 4);
-          const uint32_t b_lo = b_lo0 + stage * (S::kBBytes >> 4);
-          const uint32_t sf_lo = sf_lo0 + stage * (S::kSfBytes >> 4);
-          if (kLayer == 1 && !S::kSfInPlace) {
-            uint32_t* out = reinterpret_cast<uint32_t*>(sf_base + stage * S::kSfBytes) + 128 * h;
-            const uint32_t* in = reinterpret_cast<const uint32_t*>(sf_base + stage * S::kSfBytes) + 3 * 128;
-            uint32_t v[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) v[t] = in[src[t]];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) out[lane + 32 * t] = v[t];
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to tcgen05.cp
-            __syncwarp();
-          }
-          if (S::kSfInPlace) {
-            // In stored order the scale words of the gate rows (h = 0) occupy words [64b, 64b + 32) of the 256-word
-            // area (b = 0..3) and those of the up rows (h = 1) words [64b + 32, 64b + 64): the 128 words a warp reads
-            // are exactly the 128 it may overwrite, so the two warps never touch each other's words.  The rearranged
-            // tile is four 128-byte groups of 8 rows, 256 bytes apart, which is what the copy descriptor describes.
-            uint32_t* area = reinterpret_cast<uint32_t*>(sf_base + stage * S::kSfBytes);
-            uint32_t v[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) v[t] = area[src[t]];
-            __syncwarp();                                                  // every lane has read before any lane writes
-#pragma unroll
-            for (int t = 0; t < 4; ++t) area[64 * t + 32 * h + lane] = v[t];
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-          }
-          if (elect_one()) {
-            tc_cp_sf(sfa_col, sfa_hi | (sf_lo + (S::kSfInPlace ? 8 : 32) * h));
-            tc_cp_sf(sfb_col, sf_hi | (sf_lo + 64));
-#pragma unroll
-            for (int k = 0; k < kTileK / 32; ++k)
-              tc_mma(d, sw128_hi | (a_lo + 2 * k), sw128_hi | (b_lo + 2 * k),
-                     idesc0 + k * ((1u << 4) | (1u << 29)),               // scale byte k of both operands
-                     sfa_col, sfb, (kb | k) != 0 ? 1u : 0u);
-            tc_commit(empty0 + 8 * stage);            // shared memory of this stage is free once these MMAs retire
-          }
-          __syncwarp();
-          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
-        }
-        if (ok && elect_one()) tc_commit(smem_u32(&ctl->tmem_full[acc_stage]));
-        __syncwarp();
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------------------------------------ epilogue
-    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
-    uint32_t it = 0;
-    bool ok = true;
-    for (int64_t task = blockIdx.x; task < num_tasks && ok; task += gridDim.x, ++it) {
-      const Tile tile = tiles[task / p.n_blocks];
-      const int nb = static_cast<int>(task % p.n_blocks);
-      const bool shared = tile.expert == kSharedExpert;
-      const uint32_t acc_stage = it & 1u, acc_phase = (it >> 1) & 1u;
-      // Per-token side data of the tile (top-k weight / destination row), one coalesced load per 32 tokens issued
-      // before the accumulator is awaited; tokens read it by shuffle.
-      float wv[4] = {1.0f, 1.0f, 1.0f, 1.0f};
-      int dv[4] = {0, 0, 0, 0};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int i = 32 * c + lane;
-        if (i < tile.n_valid) {
-          if (kLayer == 1) { if (!shared) wv[c] = __ldg(p.pool_w + tile.row0 + i); }
-          else if (!kFused) dv[c] = shared ? tile.row0 + i : __ldg(p.pool_dst + tile.row0 + i);
-          else if (shared) dv[c] = static_cast<int>((32u << kOutSlotShift) | static_cast<uint32_t>(tile.row0 + i));
-          else {
-            const int r = __ldg(p.pool_dst + tile.row0 + i);       // receive-order row
-            int sr = 0;
-            while (sr + 1 < p.num_ranks && r >= ctl->rank_off[sr + 1]) ++sr;
-            dv[c] = static_cast<int>((static_cast<uint32_t>(sr) << kOutSlotShift) |
-                                     static_cast<uint32_t>(ctl->home_base[sr] + r - ctl->rank_off[sr]));
-          }
-        }
-      }
-      if (!waiter.wait_warp(smem_u32(&ctl->tmem_full[acc_stage]), acc_phase)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t d0 = tmem_base + lane_sel + acc_stage * S::kAccCols;
-      const int n16 = (tile.n_valid + 15) & ~15;
-      if (kLayer == 1) {
-        const int row = nb * kTileRows + q * 32 + lane;       // channel
-        uint8_t* act = shared ? p.act_shared : p.act_routed;
-        uint8_t* act_sf = shared ? p.act_sf_shared : p.act_sf_routed;
-        const int64_t sf_rows = shared ? p.act_sf_rows_shared : p.act_sf_rows_routed;
-        // scale byte of (token i, channel group nb*4+q): word nb of the chunk row, byte q
-        uint8_t* sf_out = act_sf + ((int64_t)nb * sf_rows + (int64_t)tile.sf_chunk * kChunkRows) * 4 + q;
-        uint8_t* act_col = act + (int64_t)tile.row0 * p.inter + row;
-        for (int i0 = 0; i0 < n16; i0 += 16) {
-          uint32_t g[16], u[16];
-          tc_ld16(d0 + i0, g);
-          tc_ld16(d0 + S::kNCap + i0, u);
-          tc_ld_wait();
-          const int c = i0 >> 5;
-          const float wcur = c == 0 ? wv[0] : (c == 1 ? wv[1] : (c == 2 ? wv[2] : wv[3]));
-          int my_sf = 0;
-          // branch-free over the 16 columns so that their dependency chains interleave (the fast-math choice is made
-          // once per batch, not per element); padding columns compute garbage that is never stored
-          auto batch = [&](auto fast) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float wt = __shfl_sync(0xffffffffu, wcur, (i0 & 16) + j);
-              const float a = swiglu_act_t<decltype(fast)::value>(__uint_as_float(g[j]), __uint_as_float(u[j]), wt, p.clamp);
-              const float amax = warp_max_nonneg(fabsf(a));
-              const int sf_exp = ue8m0_exp_of_amax(amax);
-              g[j] = float_to_e4m3(__fmul_rn(a, ue8m0_inv(sf_exp)));
-              if (lane == j) my_sf = sf_exp;
-            }
-          };
-          if (p.fast_math != 0) batch(std::true_type{});
-          else batch(std::false_type{});
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (i0 + j < tile.n_valid) act_col[(int64_t)(i0 + j) * p.inter] = static_cast<uint8_t>(g[j]);
-          if (lane < 16 && i0 + lane < tile.n_valid)
-            sf_out[chunk_pos(tile.sf_col * 32 + i0 + lane) * 4] = static_cast<uint8_t>(my_sf);
-        }
-      } else if (!kFused) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int row = nb * 2 * kTileRows + h * kTileRows + q * 32 + lane;     // output feature
-          __nv_bfloat16* out = (shared ? p.shared_out : p.ret) + row;
-          for (int i0 = 0; i0 < n16; i0 += 16) {
-            uint32_t v[16];
-            tc_ld16(d0 + h * S::kNCap + i0, v);
-            tc_ld_wait();
-            const int c = i0 >> 5;
-            const int dcur = c == 0 ? dv[0] : (c == 1 ? dv[1] : (c == 2 ? dv[2] : dv[3]));
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int dst = __shfl_sync(0xffffffffu, dcur, (i0 & 16) + j);
-              if (i0 + j < tile.n_valid) out[(int64_t)dst * p.hidden] = __float2bfloat16_rn(__uint_as_float(v[j]));
-            }
-          }
-        }
-      } else {
-        // one destination per token: resolve the 16 row pointers of a batch once, use them for both weight blocks
-        const int row0 = nb * 2 * kTileRows + q * 32 + lane;                      // output feature of weight block 0
-        for (int i0 = 0; i0 < n16; i0 += 16) {
-          uint32_t v0[16], v1[16];
-          tc_ld16(d0 + i0, v0);
-          tc_ld16(d0 + S::kNCap + i0, v1);
-          const int c = i0 >> 5;
-          const int dcur = c == 0 ? dv[0] : (c == 1 ? dv[1] : (c == 2 ? dv[2] : dv[3]));
-          tc_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t dst = static_cast<uint32_t>(__shfl_sync(0xffffffffu, dcur, (i0 & 16) + j));
-            if (i0 + j < tile.n_valid) {
-              __nv_bfloat16* out = ctl->out_base[dst >> kOutSlotShift] +
-                                   (int64_t)(dst & ((1u << kOutSlotShift) - 1u)) * p.hidden + row0;
-              out[0] = __float2bfloat16_rn(__uint_as_float(v0[j]));
-              out[kTileRows] = __float2bfloat16_rn(__uint_as_float(v1[j]));
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->tmem_empty[acc_stage]));
-    }
-  }
-
-  // ---------------------------------------------------------------------------------------------------- teardown
+__device__ __forceinline__ void sa_teardown(Control* ctl, uint32_t tmem_base) {
   __syncwarp();
   if (ctl->abort_flag != 0) {
     // abandoned call: give copies that are still in flight time to land in this CTA's shared memory before it exits
@@ -464,9 +471,56 @@ __global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) {
+  if ((threadIdx.x >> 5) == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+}
+
+// One layer per launch.
+template <int kLayer, int kBoxRows, bool kFused = false>
+__global__ void __launch_bounds__(kThreads, 1) umma_kernel(const __grid_constant__ UmmaParams p) {
+  static_assert(!kFused || kLayer == 2, "only GEMM2 writes rows back");
+  using L = Shape<kLayer, kBoxRows>;
+  extern __shared__ uint8_t smem_raw[];
+  Cta c = sa_carve<L>(smem_raw);
+  Control* ctl = c.ctl;
+  const int warp = threadIdx.x >> 5;
+  chain_release();
+  sa_setup<L>(ctl);
+  // Everything above touches only this CTA's own shared and tensor memory, so it may run while the kernel before this
+  // one in the stream is still running; everything below reads what that kernel wrote.
+  chain_wait();
+  if (kFused) {
+    if (threadIdx.x == 0) ctl->out_base[32] = p.shared_out;
+    const int t = threadIdx.x - 32;
+    if (t >= 0 && t < p.num_ranks) {
+      ctl->out_base[t] = p.ep_ret_recv[t];
+      int b = 0;
+      for (int d = 0; d < p.ep_me; ++d) b += p.ep_totals[t * 32 + d];
+      ctl->home_base[t] = b;
+    }
+    if (threadIdx.x == 64) {
+      int run = 0;
+      for (int sr = 0; sr < p.num_ranks; ++sr) { ctl->rank_off[sr] = run; run += p.ep_totals[sr * 32 + p.ep_me]; }
+      ctl->rank_off[p.num_ranks] = run;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  c.tmem_base = ctl->tmem_base;
+  c.num_stages = static_cast<uint32_t>(p.num_stages);
+  const TaskList tl = task_list(p);
+  Waiter waiter{&ctl->abort_flag, p.status, global_timer() + static_cast<uint64_t>(p.timeout_ns), kLayer, warp};
+  RoleState st;
+  if (warp == 0) {
+    if ((threadIdx.x & 31) == 0) sa_producer<kLayer, kBoxRows, L>(p, c, tl, waiter, st);
+  } else if (warp == 1 || warp == 6) {
+    sa_mma<kLayer, kBoxRows, L>(p, c, tl, waiter, st, warp == 1 ? 0 : 1);
+  } else {
+    sa_epilogue<kLayer, kBoxRows, L, kFused>(p, c, tl, waiter, st);
+  }
+  sa_teardown(ctl, c.tmem_base);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
