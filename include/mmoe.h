@@ -225,7 +225,9 @@ int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t
  * on `stream` (fork / join with events, capturable); same result as the separate calls.  Up to 128 tokens the call is
  * one stream and five or six launches: one block orders the routes, builds the plan and (up to 128 routes) places the
  * rows; the kernels are launched as a programmatic chain, so that each one's launch and set-up overlap its
- * predecessor (MMOE_DISABLE_CHAINED_LAUNCH=1 in the environment, read once per process: ordinary launches). */
+ * predecessor (MMOE_DISABLE_CHAINED_LAUNCH=1 in the environment, read once per process: ordinary launches).
+ * Threading: the second stream and its two events exist once per device; call mmoe_forward / mmoe_forward_ep for one
+ * device from one host thread at a time. */
 int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
                  void* y_bf16, int32_t num_tokens, int32_t block_m, int32_t* stats, void* stream);
 

@@ -35,7 +35,9 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 const int kBlockMs[6] = {16, 32, 64, 128, 192, 240};
 
-// A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.
+// A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.  One lane per
+// device, shared by every caller: two host threads must not run mmoe_forward / mmoe_forward_ep on the same device at
+// the same time (their fork / join event pairs would interleave).
 struct SideLane {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
@@ -54,8 +56,11 @@ SideLane* side_lane(bool may_create) {
     SideLane n;
     if (cudaStreamCreateWithFlags(&n.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&n.fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&n.join, cudaEventDisableTiming) != cudaSuccess)
+        cudaEventCreateWithFlags(&n.join, cudaEventDisableTiming) != cudaSuccess) {
+      if (n.fork != nullptr) cudaEventDestroy(n.fork);
+      cudaStreamDestroy(n.stream);
       return nullptr;
+    }
     l = n;
   }
   return l.stream != nullptr ? &l : nullptr;
