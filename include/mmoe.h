@@ -153,6 +153,8 @@ typedef struct MmoeOptions {
   int32_t engine;           /* 0: tcgen05 tensor-core kernels; 1: scalar validation kernels (tests only) */
   int32_t timeout_ms;       /* bound of every device-side wait; <= 0 selects the default (2000) */
   int32_t layer_mask;       /* 0 or 3: both grouped GEMMs; 1: GEMM1 (+SwiGLU) only; 2: GEMM2 only (per-kernel timing) */
+  const void* residual;     /* mmoe_forward / mmoe_forward_ep: optional bf16 [num_tokens, H] added in the combine
+                             * (see mmoe_combine_residual); NULL: none */
 } MmoeOptions;
 
 /* The steps of one forward call.  At EP1 `mmoe_forward` runs all of them; at EP>1 the host interleaves the three
@@ -220,6 +222,12 @@ int mmoe_experts_ep_return(const MmoeGeometry* geo, void* workspace, const void*
                            void* stream);
 /* y[t] = bf16(sum of the token's valid slots in ascending order, shared expert last). */
 int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream);
+/* The same with the residual stream of the decoder layer added in the same pass (the addition the serving engine makes
+ * right after the layer): y[t] = bf16(float(bf16(sum)) + float(residual[t])), i.e. bit for bit what a separate BF16
+ * addition of the layer output and `residual_bf16` ([num_tokens, H], 16-byte aligned, may alias y) leaves.  Saves
+ * one read and one write of [num_tokens, H].  NULL residual: plain combine. */
+int mmoe_combine_residual(const MmoeGeometry* geo, void* workspace, void* y_bf16, const void* residual_bf16,
+                          int32_t num_tokens, void* stream);
 /* EP1 convenience: count, place, experts, combine.  Past the decode sizes (num_tokens > 128, with a shared expert) the
  * routed experts' ordering, plan and placement run on the library's second stream while the shared expert's GEMMs run
  * on `stream` (fork / join with events, capturable); same result as the separate calls.  Up to 128 tokens the call is

@@ -143,6 +143,32 @@ def test_masked_tokens_padding_and_empty_call():
     assert y_empty.shape == (0, layer.hidden)
 
 
+@pytest.mark.parametrize("m", [1, 40, 300])
+def test_residual_added_in_the_combine_pass(m):
+    """``residual=`` gives bit for bit what a separate BF16 addition after the layer gives, also in place (residual is y),
+    at decode and prefill sizes (chained small-call path and the two-stream path)."""
+    from vllm_plugin_b200 import api
+    layer = H.make_layer(shared=True, seed=12, **SMALL)
+    hid = O.make_hidden(m, layer.hidden, 5)
+    ids, w = O.make_routing(m, layer.num_experts, layer.num_topk, 6, mask_frac=0.1)
+    y, buf = H.run_layer(layer, hid, ids, w)
+    dev = y.device
+    res = (torch.randn(m, layer.hidden, generator=torch.Generator().manual_seed(3)) * 2).to(torch.bfloat16).to(dev)
+    want = y + res                                           # the engine's own addition
+    l1, l2, sl1, sl2 = H.kernel_weights(layer, dev)
+    out = torch.empty_like(y)
+    api.stage_inputs_for_mega_moe(buf, hid.to(dev), ids.to(dev), w.to(dev))
+    api.fp8_fp4_mega_moe(out, l1, l2, buf, sl1, sl2, activation_clamp=10.0, residual=res)
+    assert torch.equal(out, want)
+    inplace = res.clone()
+    api.fp8_fp4_mega_moe(inplace, l1, l2, buf, sl1, sl2, activation_clamp=10.0, residual=inplace)
+    assert torch.equal(inplace, want)
+    api.fp8_fp4_mega_moe(out, l1, l2, buf, sl1, sl2, activation_clamp=10.0)        # and none again: the plain output
+    assert torch.equal(out, y)
+    with pytest.raises(AssertionError):
+        api.fp8_fp4_mega_moe(out, l1, l2, buf, sl1, sl2, activation_clamp=10.0, residual=res.float())
+
+
 def test_outputs_do_not_depend_on_batch_composition():
     """Size-independent property: a token's output is bit-identical whatever other tokens share the call (columns of the
     tensor-core tiles are independent and the K order is fixed)."""

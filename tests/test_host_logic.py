@@ -105,7 +105,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(_native.library_path())
     for name in declared:
         assert hasattr(lib, name), name
-    assert _native.load().mmoe_abi_version() == 2
+    assert _native.load().mmoe_abi_version() == 3
 
 
 def test_layout_is_consistent():

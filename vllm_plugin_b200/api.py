@@ -37,13 +37,14 @@ def fp8_fp4_mega_moe(y, l1_weights: Tuple[Any, Any], l2_weights: Tuple[Any, Any]
                      shared_l2_weights: Optional[Tuple[Any, Any]] = None, cumulative_local_expert_recv_stats=None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
                      activation_clamp: Optional[float] = None, fast_math: bool = True, activation_alpha: float = 1.0,
-                     activation_beta: float = 0.0):
-    """Fused MegaMoE for one rank.  The BLOCK_M variant is selected from ``y.size(0)`` of this call."""
+                     activation_beta: float = 0.0, *, residual=None):
+    """Fused MegaMoE for one rank.  The BLOCK_M variant is selected from ``y.size(0)`` of this call.  ``residual``
+    (keyword only, an addition to the reference's signature): BF16 ``(M, H)`` added to the output in the combine pass."""
     from .backend.frontend import fp8_fp4_mega_moe as _impl
 
     return _impl(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights,
                  cumulative_local_expert_recv_stats, recipe, activation, activation_clamp, fast_math, activation_alpha,
-                 activation_beta)
+                 activation_beta, residual=residual)
 
 
 def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_tokens: int,

@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "mmoe_last_error", "mmoe_abi_version", "mmoe_set_tuning", "mmoe_route_order_noalloc", "mmoe_ep_dispatch", "mmoe_ep_return",
     "mmoe_experts_ep_return", "mmoe_forward_ep", "mmoe_transform_weights",
     "mmoe_plan_shared", "mmoe_experts_select", "mmoe_route_stage_inputs", "mmoe_stage_inputs_nvfp4",
+    "mmoe_combine_residual",
 )
 
 
@@ -59,7 +60,7 @@ class MmoeWeights(ctypes.Structure):
 
 class MmoeOptions(ctypes.Structure):
     _fields_ = [("activation_clamp", ctypes.c_float), ("fast_math", ctypes.c_int32), ("engine", ctypes.c_int32),
-                ("timeout_ms", ctypes.c_int32), ("layer_mask", ctypes.c_int32)]
+                ("timeout_ms", ctypes.c_int32), ("layer_mask", ctypes.c_int32), ("residual", ctypes.c_void_p)]
 
 
 _lib: Optional[ctypes.CDLL] = None
@@ -92,6 +93,7 @@ def load() -> ctypes.CDLL:
     lib.mmoe_dispatch_place.argtypes = [geo_p, vp, i32, i32, vp, vp]
     lib.mmoe_experts.argtypes = [geo_p, vp, ctypes.POINTER(MmoeWeights), ctypes.POINTER(MmoeOptions), i32, i32, vp]
     lib.mmoe_combine.argtypes = [geo_p, vp, vp, i32, vp]
+    lib.mmoe_combine_residual.argtypes = [geo_p, vp, vp, vp, i32, vp]
     lib.mmoe_forward.argtypes = [geo_p, vp, ctypes.POINTER(MmoeWeights), ctypes.POINTER(MmoeOptions), vp, i32, i32, vp, vp]
     lib.mmoe_read_status.argtypes = [geo_p, vp, ctypes.POINTER(i32), vp]
     lib.mmoe_status_string.argtypes = [i32]

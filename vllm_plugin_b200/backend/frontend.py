@@ -288,9 +288,13 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
                      cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
                      activation_clamp: Optional[float] = None, fast_math: bool = True, activation_alpha: float = 1.0,
-                     activation_beta: float = 0.0) -> None:
+                     activation_beta: float = 0.0, *, residual: Optional[torch.Tensor] = None) -> None:
     """One MegaMoE layer call for this rank: reads the staged inputs of ``sym_buffer`` (first ``y.size(0)`` tokens),
-    writes ``y``.  Launches on the current stream and never synchronises (the host-driven NCCL transport aside)."""
+    writes ``y``.  Launches on the current stream and never synchronises (the host-driven NCCL transport aside).
+
+    ``residual`` (not in the reference's signature; keyword only): BF16 ``(M, H)`` added to the layer output inside the
+    combine pass, ``y = bf16(bf16(layer output) + residual)`` -- bit for bit what the engine's separate addition after the
+    layer leaves; it may be ``y`` itself."""
     stats = cumulative_local_expert_recv_stats
     tensors = (l1_weights[0], l1_weights[1], l2_weights[0], l2_weights[1],
                shared_l1_weights[0] if shared_l1_weights is not None else None,
@@ -311,6 +315,10 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
         assert y.is_cuda and y.data_ptr() % 16 == 0, "y must be a 16-byte aligned CUDA tensor"
         assert m <= sym_buffer.num_max_tokens_per_rank, "num_tokens must be <= num_max_tokens_per_rank"
         assert activation_clamp is None or activation_clamp > 0, "activation_clamp must be positive"
+    if residual is not None:
+        assert residual.shape == y.shape and residual.dtype == torch.bfloat16 and residual.is_contiguous(), \
+            "residual must be contiguous BF16 (M, H)"
+        assert residual.device == y.device and residual.data_ptr() % 16 == 0, "residual must be a 16-byte aligned tensor on y's device"
     ko = _kernel_options
     key = (activation_clamp, bool(fast_math), _engine, ko.timeout_ms)
     if rec.options_key != key:
@@ -332,6 +340,8 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
     lib = _native.load()
     bm = get_block_m_for_mega_moe(sym_buffer.num_ranks, sym_buffer.num_experts, sym_buffer.num_max_tokens_per_rank, m,
                                   sym_buffer.num_topk, sym_buffer.mma_type)
+    rec.options.residual = residual.data_ptr() if residual is not None and m > 0 else None
+    res_ptr = rec.options.residual
     w, opts = ctypes.byref(rec.weights), ctypes.byref(rec.options)
     stats_ptr = stats.data_ptr() if stats is not None else None
     stream = torch.cuda.current_stream(y.device).cuda_stream
@@ -350,7 +360,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
             _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
             _native.check(lib.mmoe_experts(g, ws, w, opts, m, bm, stream))
             _native.check(lib.mmoe_ep_return(g, ws, peers, opts, stream))
-            _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
+            _native.check(lib.mmoe_combine_residual(g, ws, y.data_ptr(), res_ptr, m, stream))
     else:
         group = sym_buffer.group
         _native.check(lib.mmoe_dispatch_count(g, ws, m, stream))
@@ -362,7 +372,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer, shared
         _native.check(lib.mmoe_dispatch_place(g, ws, m, bm, stats_ptr, stream))
         _native.check(lib.mmoe_experts(g, ws, w, opts, m, bm, stream))
         exchange_rows(group, sym_buffer.ret_recv, sym_buffer.ret, send_splits, recv_splits)
-        _native.check(lib.mmoe_combine(g, ws, y.data_ptr(), m, stream))
+        _native.check(lib.mmoe_combine_residual(g, ws, y.data_ptr(), res_ptr, m, stream))
     if poll is not None:
         poll.after_call(sym_buffer, ko.status_poll_interval)
 

@@ -35,9 +35,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 const int kBlockMs[6] = {16, 32, 64, 128, 192, 240};
 
-// A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.  One lane per
-// device, shared by every caller: two host threads must not run mmoe_forward / mmoe_forward_ep on the same device at
-// the same time (their fork / join event pairs would interleave).
+// A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.
 struct SideLane {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
@@ -56,11 +54,8 @@ SideLane* side_lane(bool may_create) {
     SideLane n;
     if (cudaStreamCreateWithFlags(&n.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&n.fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&n.join, cudaEventDisableTiming) != cudaSuccess) {
-      if (n.fork != nullptr) cudaEventDestroy(n.fork);
-      cudaStreamDestroy(n.stream);
+        cudaEventCreateWithFlags(&n.join, cudaEventDisableTiming) != cudaSuccess)
       return nullptr;
-    }
     l = n;
   }
   return l.stream != nullptr ? &l : nullptr;
@@ -144,7 +139,7 @@ float bf16_round_host(float v) {
 
 extern "C" {
 
-int mmoe_abi_version(void) { return 2; }
+int mmoe_abi_version(void) { return 3; }
 
 int mmoe_set_tuning(int32_t max_stages, int32_t orientation) {
   if (max_stages < 0 || max_stages == 1) return fail(MMOE_ERR_INVALID_ARGUMENT, "max_stages=%d must be 0 or >= 2", max_stages);
@@ -523,7 +518,8 @@ int run_experts(const MmoeGeometry* geo, void* workspace, const void* const* pee
 }
 }  // namespace
 
-int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream) {
+int mmoe_combine_residual(const MmoeGeometry* geo, void* workspace, void* y_bf16, const void* residual_bf16,
+                          int32_t num_tokens, void* stream) {
   mmoe::Ctx c;
   int rc = make_ctx(geo, workspace, &c);
   if (rc != MMOE_OK) return rc;
@@ -531,8 +527,14 @@ int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t
   if (rc != MMOE_OK) return rc;
   if (num_tokens > 0 && (y_bf16 == nullptr || (reinterpret_cast<uintptr_t>(y_bf16) & 15u) != 0))
     return fail(MMOE_ERR_INVALID_ARGUMENT, "y must be a 16-byte aligned device pointer");
-  cudaError_t e = mmoe::launch_combine(c, y_bf16, num_tokens, static_cast<cudaStream_t>(stream));
+  if ((reinterpret_cast<uintptr_t>(residual_bf16) & 15u) != 0)
+    return fail(MMOE_ERR_INVALID_ARGUMENT, "the residual must be a 16-byte aligned device pointer");
+  cudaError_t e = mmoe::launch_combine(c, y_bf16, residual_bf16, num_tokens, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MMOE_OK : cuda_fail(e, "combine launch");
+}
+
+int mmoe_combine(const MmoeGeometry* geo, void* workspace, void* y_bf16, int32_t num_tokens, void* stream) {
+  return mmoe_combine_residual(geo, workspace, y_bf16, nullptr, num_tokens, stream);
 }
 
 int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* weights, const MmoeOptions* opt,
@@ -570,7 +572,7 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
   if (lane == nullptr) {
     rc = dispatch(stream);
     if (rc == MMOE_OK) rc = mmoe_experts(geo, workspace, weights, opt, num_tokens, block_m, stream);
-    if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+    if (rc == MMOE_OK) rc = mmoe_combine_residual(geo, workspace, y_bf16, opt != nullptr ? opt->residual : nullptr, num_tokens, stream);
     return rc;
   }
   // The shared expert needs only the staged tokens: its two GEMMs run here while the routed experts' ordering, plan
@@ -588,7 +590,7 @@ int mmoe_forward(const MmoeGeometry* geo, void* workspace, const MmoeWeights* we
   mmoe::break_chain();                      // the next kernel has two predecessors: launch it without the attribute
   if (rc_side != MMOE_OK) return rc_side;
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 1);
-  if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+  if (rc == MMOE_OK) rc = mmoe_combine_residual(geo, workspace, y_bf16, opt != nullptr ? opt->residual : nullptr, num_tokens, stream);
   return rc;
 }
 
@@ -612,7 +614,7 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
     rc = mmoe_ep_dispatch(geo, workspace, peer_workspaces, num_tokens, opt, stream);
     if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
     if (rc == MMOE_OK) rc = run_experts(geo, workspace, peer_workspaces, weights, opt, num_tokens, block_m, stream, 0);
-    if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+    if (rc == MMOE_OK) rc = mmoe_combine_residual(geo, workspace, y_bf16, opt != nullptr ? opt->residual : nullptr, num_tokens, stream);
     return rc;
   }
 #if MMOE_EP_TRACE
@@ -648,7 +650,7 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   EP_TR(4, main_stream);
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, peer_workspaces, weights, opt, num_tokens, block_m, stream, 1);
   EP_TR(5, main_stream);
-  if (rc == MMOE_OK) rc = mmoe_combine(geo, workspace, y_bf16, num_tokens, stream);
+  if (rc == MMOE_OK) rc = mmoe_combine_residual(geo, workspace, y_bf16, opt != nullptr ? opt->residual : nullptr, num_tokens, stream);
   EP_TR(6, main_stream);
 #if MMOE_EP_TRACE
   cudaStreamSynchronize(main_stream);

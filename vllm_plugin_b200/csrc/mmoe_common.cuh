@@ -251,7 +251,7 @@ cudaError_t launch_pack(const Ctx& c, int m, cudaStream_t s);
 cudaError_t launch_route_plan_place_small(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
 cudaError_t launch_plan_place(const Ctx& c, int m, int block_m, int32_t* stats, cudaStream_t s);
 cudaError_t launch_shared_plan(const Ctx& c, int m, int block_m, cudaStream_t s);
-cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s);
+cudaError_t launch_combine(const Ctx& c, void* y, const void* residual, int m, cudaStream_t s);
 cudaError_t launch_experts_simt(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 cudaError_t launch_experts_umma(const Ctx& c, const MmoeWeights& w, const MmoeOptions& o, int m, int block_m, cudaStream_t s);
 int prepare_umma(const MmoeGeometry& geo);   // returns an MMOE_* code

@@ -874,7 +874,7 @@ __device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
 
 __global__ void __launch_bounds__(256) combine_kernel(
     const uint4* __restrict__ rows, const int32_t* __restrict__ route_pos, const uint4* __restrict__ shared_out,
-    uint4* __restrict__ y, int m, int h, int k) {
+    const uint4* __restrict__ residual, uint4* __restrict__ y, int m, int h, int k) {
   chain_begin();
   const int vec = h / 8;
   const int64_t total = (int64_t)m * vec;
@@ -891,18 +891,30 @@ __global__ void __launch_bounds__(256) combine_kernel(
     __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    if (residual != nullptr) {
+      // what the serving engine's separate BF16 addition leaves: the layer output rounded to BF16 first, then the sum
+      // of the two BF16 values rounded once more
+      const uint4 res = residual[i];
+      const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&res);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(o[j]), b = __bfloat1622float2(r[j]);
+        o[j] = __floats2bfloat162_rn(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+      }
+    }
     y[i] = out;
   }
 }
 
-cudaError_t launch_combine(const Ctx& c, void* y, int m, cudaStream_t s) {
+cudaError_t launch_combine(const Ctx& c, void* y, const void* residual, int m, cudaStream_t s) {
   if (m == 0) return cudaSuccess;
   const int64_t total = (int64_t)m * c.geo.hidden / 8;
   const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
   const uint4* rows = c.geo.num_ranks == 1 ? c.at<uint4>(c.lay.ret) : c.at<uint4>(c.lay.ret_recv);
   launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, s, rows, c.at<int32_t>(c.lay.route_pos),
                                         c.geo.num_shared_experts > 0 ? c.at<uint4>(c.lay.shared_out) : nullptr,
-                                        static_cast<uint4*>(y), m, c.geo.hidden, c.geo.num_topk);
+                                        static_cast<const uint4*>(residual), static_cast<uint4*>(y), m, c.geo.hidden,
+                                        c.geo.num_topk);
   return cudaGetLastError();
 }
 
