@@ -380,7 +380,11 @@ def run_ours(args):
     sp = stream.cuda_stream
     ws = buf.base_ptr
     peers = (ctypes.c_void_p * world)(*buf.peer_ptrs) if world > 1 and buf.peer_ptrs is not None else None
-    names = ["stage", "order", "exchange", "place", "gemm1", "gemm2", "return", "combine"]
+    # past 128 tokens the product call runs the shared expert as launches of its own (tiles planned from the token
+    # count alone) and the routed experts as one launch per GEMM; the phases are timed in that structure
+    split = m > 128
+    opts0 = _native.MmoeOptions(10.0, 1, 0, 2000, 0)
+    names = ["stage", "order", "exchange", "place", "shared", "gemm1", "gemm2", "return", "combine"]
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
     acc = {n: [] for n in names}
     can_time_phases = world == 1 or peers is not None
@@ -395,15 +399,25 @@ def run_ours(args):
         evs[3].record(stream)
         _native.check(lib.mmoe_dispatch_place(geo, ws, m, bm, None, sp))
         evs[4].record(stream)
-        _native.check(lib.mmoe_experts(geo, ws, ctypes.byref(wst), ctypes.byref(opts1), m, bm, sp))
+        if split:
+            _native.check(lib.mmoe_plan_shared(geo, ws, m, bm, sp))
+            _native.check(lib.mmoe_experts_select(geo, ws, ctypes.byref(wst), ctypes.byref(opts0), m, bm, 2, sp))
         evs[5].record(stream)
-        _native.check(lib.mmoe_experts(geo, ws, ctypes.byref(wst), ctypes.byref(opts2), m, bm, sp))
+        if split:
+            _native.check(lib.mmoe_experts_select(geo, ws, ctypes.byref(wst), ctypes.byref(opts1), m, bm, 1, sp))
+        else:
+            _native.check(lib.mmoe_experts(geo, ws, ctypes.byref(wst), ctypes.byref(opts1), m, bm, sp))
         evs[6].record(stream)
+        if split:
+            _native.check(lib.mmoe_experts_select(geo, ws, ctypes.byref(wst), ctypes.byref(opts2), m, bm, 1, sp))
+        else:
+            _native.check(lib.mmoe_experts(geo, ws, ctypes.byref(wst), ctypes.byref(opts2), m, bm, sp))
+        evs[7].record(stream)
         if world > 1:
             _native.check(lib.mmoe_ep_return(geo, ws, peers, ctypes.byref(opts1), sp))
-        evs[7].record(stream)
-        _native.check(lib.mmoe_combine(geo, ws, y.data_ptr(), m, sp))
         evs[8].record(stream)
+        _native.check(lib.mmoe_combine(geo, ws, y.data_ptr(), m, sp))
+        evs[9].record(stream)
         torch.cuda.synchronize(dev)
         if it >= 3:
             for j, n in enumerate(names):
@@ -430,6 +444,7 @@ def run_ours(args):
               2: "tokens-as-A", 3: "tokens-as-A"}[args.orientation]
     kernel_name = ("tm_kernel<1> (grouped GEMM1 + SwiGLU/requant, tokens-as-A)" if family == "tokens-as-A"
                    else "umma_kernel<1> (grouped GEMM1 + SwiGLU/requant, weights-as-A)")
+    kernel_name += ", the launch over the routed experts' tiles" if m > 128 else ", one launch over routed and shared tiles"
     sm_mhz = float((clocks or {}).get("sm_mhz") or 0.0)
     sm_mhz = reduce_ranks(sm_mhz, "max") or 1965.0                               # rank 0 samples its GPU
     tensor_peak = 2 * TENSOR_MAC_PER_CLK_SM * NUM_SMS * sm_mhz * 1e6 / 1e12      # TFLOP/s at the sampled SM clock
@@ -438,9 +453,13 @@ def run_ours(args):
     kernels = dict(phases)
     if "gemm1_ms" in phases:
         g1_ms, g2_ms = phases["gemm1_ms"], phases["gemm2_ms"]
-        g1_flops, g2_flops = pairs_mean * 4 * I * H, pairs_mean * 2 * I * H
-        w13_bytes = distinct_mean * (I * H + 2 * I * H // 32) + (2 * I * H + 2 * I * H // 32)
-        w2_bytes = distinct_mean * (H * I // 2 + H * I // 32) + (H * I + H * I // 32)
+        # rows and weights of the timed launches: the routed experts alone when the shared expert has its own launches
+        shared_rows = 0 if split else m
+        rows = pairs_mean - m + shared_rows
+        pairs_mean = rows
+        g1_flops, g2_flops = rows * 4 * I * H, rows * 2 * I * H
+        w13_bytes = distinct_mean * (I * H + 2 * I * H // 32) + (0 if split else 2 * I * H + 2 * I * H // 32)
+        w2_bytes = distinct_mean * (H * I // 2 + H * I // 32) + (0 if split else H * I + H * I // 32)
         g1_tflops, g1_gbs = g1_flops / (g1_ms * 1e-3) / 1e12, w13_bytes / (g1_ms * 1e-3) / 1e9
         tensor_bound = g1_flops / (tensor_peak * 1e12) > w13_bytes / (peak_hbm * 1e9)
         token_side_bytes = pairs_mean * (H + H // 32 + I + I // 32)     # FP8 rows + scales in, activations + scales out
@@ -465,7 +484,9 @@ def run_ours(args):
             "gemm1_tensor_frac": g1_tflops / tensor_peak, "gemm2_tensor_frac": g2_flops / (g2_ms * 1e-3) / 1e12 / tensor_peak})
     kernels.update({
         "kernel_family": family,
-        "phase_note": "phases timed back to back on one stream; the product call overlaps ordering / exchange with the shared expert",
+        "phase_note": "phases timed back to back on one stream in the product call's launch structure (past 128 tokens: "
+                      "shared_ms = the shared expert's two GEMM launches, gemm1_ms / gemm2_ms = the routed experts' "
+                      "launches); the product call overlaps ordering / exchange with the shared expert",
         "layer_tflops_per_gpu": flops_mean / (step_ms * 1e-3) / 1e12,
         "layer_tensor_frac": flops_mean / (step_ms * 1e-3) / 1e12 / tensor_peak,
         "layer_algorithmic_gbs_per_gpu": bytes_mean / (step_ms * 1e-3) / 1e9,

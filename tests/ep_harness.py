@@ -27,6 +27,9 @@ def free_port() -> int:
 def _entry(rank, world, backend, port, fn, args, errors):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    # every rank also evaluates the CPU oracle: without a share of the cores per rank the ranks' thread pools
+    # oversubscribe the host (eight ranks took more than five minutes for seconds of work)
+    torch.set_num_threads(max(1, (os.cpu_count() or world) // world))
     try:
         from datetime import timedelta
         limit = timedelta(seconds=90)          # a rank that failed must not keep the others waiting for long
