@@ -39,8 +39,6 @@ def build(verbose: bool = False, force: bool = False) -> str:
            "-shared", "-o", lib_path()] + [os.path.join(HERE, s) for s in SOURCES]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
-    if os.environ.get("MMOE_EP_TRACE"):       # phase times of the expert-parallel forward, printed per rank (development only)
-        cmd[1:1] = ["-DMMOE_EP_TRACE=1"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

@@ -29,10 +29,6 @@ int cuda_fail(cudaError_t e, const char* what) {
   return fail(MMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
-#ifndef MMOE_EP_TRACE
-#define MMOE_EP_TRACE 0
-#endif
-
 const int kBlockMs[6] = {16, 32, 64, 128, 192, 240};
 
 // A second stream per device on which the expert-parallel dispatch runs while the shared expert computes.
@@ -617,21 +613,11 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
     if (rc == MMOE_OK) rc = mmoe_combine_residual(geo, workspace, y_bf16, opt != nullptr ? opt->residual : nullptr, num_tokens, stream);
     return rc;
   }
-#if MMOE_EP_TRACE
-  // development build: phase times of this call from timing events (synchronises at the end of every call)
-  cudaEvent_t tr[8];
-  for (auto& t : tr) cudaEventCreate(&t);
-  cudaEventRecord(tr[0], main_stream);
-#define EP_TR(i, st) cudaEventRecord(tr[i], st)
-#else
-#define EP_TR(i, st) ((void)0)
-#endif
   // fork: the exchange of counts and rows runs on the side stream ...
   cudaError_t e = cudaEventRecord(lane->fork, main_stream);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(lane->stream, lane->fork, 0);
   if (e != cudaSuccess) return cuda_fail(e, "forking the dispatch stream");
   const int rc_side = mmoe_ep_dispatch(geo, workspace, peer_workspaces, num_tokens, opt, lane->stream);
-  EP_TR(1, lane->stream);
   e = cudaEventRecord(lane->join, lane->stream);
   // ... while the shared expert, which needs only this rank's own tokens, runs both of its GEMMs here
   mmoe::Ctx c;
@@ -640,41 +626,16 @@ int mmoe_forward_ep(const MmoeGeometry* geo, void* workspace, const void* const*
   if (rc == MMOE_OK && mmoe::launch_shared_plan(c, num_tokens, block_m, main_stream) != cudaSuccess)
     rc = cuda_fail(cudaGetLastError(), "shared plan launch");
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, nullptr, weights, opt, num_tokens, block_m, stream, 2);
-  EP_TR(2, main_stream);
   // join (always, so that a capture is never left forked)
   if (e == cudaSuccess) e = cudaStreamWaitEvent(main_stream, lane->join, 0);
   if (e != cudaSuccess) return cuda_fail(e, "joining the dispatch stream");
   if (rc_side != MMOE_OK) return rc_side;
-  EP_TR(3, main_stream);
   if (rc == MMOE_OK) rc = mmoe_dispatch_place(geo, workspace, num_tokens, block_m, stats, stream);
-  EP_TR(4, main_stream);
   if (rc == MMOE_OK) rc = run_experts(geo, workspace, peer_workspaces, weights, opt, num_tokens, block_m, stream, 1);
-  EP_TR(5, main_stream);
   if (rc == MMOE_OK) rc = mmoe_combine_residual(geo, workspace, y_bf16, opt != nullptr ? opt->residual : nullptr, num_tokens, stream);
-  EP_TR(6, main_stream);
-#if MMOE_EP_TRACE
-  cudaStreamSynchronize(main_stream);
-  {
-    static double acc[6] = {0, 0, 0, 0, 0, 0};
-    static int calls = 0;
-    float ms[6];
-    cudaEventElapsedTime(&ms[0], tr[0], tr[1]);   // fork -> dispatch done (side stream)
-    cudaEventElapsedTime(&ms[1], tr[0], tr[2]);   // fork -> shared GEMMs done
-    cudaEventElapsedTime(&ms[2], tr[0], tr[3]);   // fork -> join
-    cudaEventElapsedTime(&ms[3], tr[3], tr[4]);   // place
-    cudaEventElapsedTime(&ms[4], tr[4], tr[5]);   // routed GEMMs + barrier 2
-    cudaEventElapsedTime(&ms[5], tr[5], tr[6]);   // combine
-    if (calls >= 8) for (int i = 0; i < 6; ++i) acc[i] += ms[i];
-    if (++calls == 28)
-      printf("rank %d: dispatch %.0f us | shared GEMMs %.0f | join at %.0f | place %.0f | routed+barrier %.0f | combine %.0f\n",
-             geo->rank, acc[0] * 50, acc[1] * 50, acc[2] * 50, acc[3] * 50, acc[4] * 50, acc[5] * 50);
-    for (auto& t : tr) cudaEventDestroy(t);
-  }
-#endif
   return rc;
 }
 
-#undef EP_TR
 
 int mmoe_transform_weights(const void* w_in, void* w_out, const int32_t* sf_in, int32_t* sf_out, int32_t num_groups,
                            int32_t rows, int32_t k_packed_bytes, int32_t k_words, int32_t interleave, void* stream) {
