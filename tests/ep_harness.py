@@ -84,6 +84,17 @@ def run_ranks(world: int, backend: str, fn, *args, timeout: float = 600.0) -> No
 # ---------------------------------------------------------------------------------------------------------------------
 # rank bodies (module level so that spawn can pickle them)
 # ---------------------------------------------------------------------------------------------------------------------
+def agreement_body(rank, world, failing_rank):
+    """The outcome of the symmetric allocation is agreed on by the whole group: one failing rank turns the peer-memory
+    transport off everywhere; without a failure everyone keeps it."""
+    from vllm_plugin_b200.backend.workspace import everyone_succeeded
+
+    group = dist.group.WORLD
+    cpu = torch.device("cpu")
+    assert everyone_succeeded(group, rank != failing_rank, cpu) is (failing_rank < 0)
+    assert everyone_succeeded(group, True, cpu) is True
+
+
 def exchange_body(rank, world, num_experts, k, tokens_per_rank, seed):
     """Host logic of the EP exchanges on CPU tensors: what each rank receives and in which order, and that the return
     exchange puts every row back where its route expects it."""

@@ -24,6 +24,22 @@ from .heuristics import TOKEN_ALIGNMENT, align
 _SUPPORTED_ACTIVATIONS = ("swiglu",)
 
 
+def everyone_succeeded(group, ok: bool, device) -> bool:
+    """True only if ``ok`` is true on every rank of ``group`` (a MIN all-reduce of one flag): the choice between the
+    peer-memory exchange and the NCCL one must come out the same on all ranks.  A group that cannot reduce (a test
+    double) keeps this rank's own outcome."""
+    try:
+        import torch.distributed as dist
+
+        if isinstance(group, dist.ProcessGroup):
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            return bool(flag.item())
+    except Exception:  # noqa: BLE001
+        pass
+    return ok
+
+
 class SymmBuffer:
     """Workspace of one (group, geometry).  Created through :func:`get_symm_buffer_for_mega_moe`."""
 
@@ -79,16 +95,7 @@ class SymmBuffer:
             assert self.peer_ptrs[group.rank()] == self.buffer.data_ptr()
         except Exception as exc:  # noqa: BLE001 - no symmetric memory: the host-driven NCCL exchange still works
             problem = f"{type(exc).__name__}: {exc}"
-        everyone_ok = problem is None
-        try:
-            import torch.distributed as dist
-
-            if isinstance(group, dist.ProcessGroup):
-                flag = torch.tensor([1 if problem is None else 0], dtype=torch.int32, device=device)
-                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-                everyone_ok = bool(flag.item())
-        except Exception:  # noqa: BLE001 - a group that cannot reduce keeps this rank's own outcome
-            pass
+        everyone_ok = everyone_succeeded(group, problem is None, device)
         if not everyone_ok:
             warnings.warn(f"symmetric memory is unavailable ({problem or 'on another rank'}); using the NCCL exchange")
             self.peer_ptrs = None
