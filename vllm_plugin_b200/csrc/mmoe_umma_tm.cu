@@ -13,8 +13,9 @@
 //     the up value of a channel 8 columns apart in the same thread -- no de-interleaving tensor map, no shuffles, and the
 //     stored scale words (4x32 transposed per 128 stored rows) are already what tcgen05.cp wants: nothing is permuted;
 //   * the amax of 32 output channels is a reduction inside one thread;
-//   * outputs leave as 16-byte stores: 32 E4M3 bytes per scale group (layer 1), 384 contiguous BF16 bytes per task
-//     (layer 2) -- also when the row goes straight into the source rank's buffer over NVLink (kFused).
+//   * outputs leave in rows: 32 E4M3 bytes per scale group as two 16-byte stores (layer 1); layer 2 passes a block of
+//     32 rows x 64 columns through a swizzled staging area so that 8 lanes write 128 contiguous bytes of one row -- also
+//     when the row goes straight into the source rank's buffer over NVLink (kFused).
 //
 //   warp 0     tile producer: per 128-K stage one TMA box of token rows and one of weight rows (packed FP4 expands to
 //              byte containers on the way into shared memory; no cluster multicast)
@@ -34,8 +35,11 @@
 // CTA stages its own token tile and HALF of the task's weight rows (96), the pair's tensor cores read both halves; the
 // leader CTA's threads issue the scale copies and the UMMAs for both.  Both kernel families are bound by shared-memory
 // bandwidth (about 146 B/clk for TMA fills and operand reads together, measured on both): a single CTA moves 20 KB per
-// UMMA slot of 96 clk, a pair 14 KB per CTA, which is what lets the tensor pipe run at its own rate.  No load uses
-// cluster multicast: every CTA fetches its own boxes, completion crosses the pair as plain mbarrier arrivals.
+// UMMA slot of 96 clk; a pair was meant to move 14 KB per CTA, but the peer's half of the weight rows is still read out
+// of the peer's shared memory (about 17 KB per SM), and the pair's issuing thread pays two commits per stage.  Measured,
+// pairs are no faster than single CTAs at any token density, so the automatic choice never takes them (orientation 3
+// selects them).  No load uses cluster multicast: every CTA fetches its own boxes, completion crosses the pair as plain
+// mbarrier arrivals.
 //
 // The same roles exist in the reference's kernel (backend/kernel/tma_warps.py, mma_warp.py, epilogue.py).  Persistent
 // CTAs (one per SM) walk the static task list tile-major, so that the CTAs working at the same time share a token tile
